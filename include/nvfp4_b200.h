@@ -1,0 +1,108 @@
+/*
+ * nvfp4_b200.h -- C ABI of libnvfp4_b200.so, the sm_100a (B200) implementation of the
+ * NVFP4 training hot path: per-tensor amax, fused NVFP4 quantizer, block-scaled FP4 GEMM.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer owned by the caller unless a comment says "host".
+ *   - Nothing here allocates or frees device memory; work is enqueued on `stream`
+ *     (a cudaStream_t passed as void*; NULL = the legacy default stream) and the call returns
+ *     without synchronising.
+ *   - Return value: NVFP4_OK (0) or a negative NVFP4_E_* code for an argument or launch error.
+ *     Nothing throws.  nvfp4_status_string() names a code.
+ *   - Data formats are those of the reference's NVFP4Tensor (nvfp4_gemm.py:45-48):
+ *       qdata   uint8 [rows, K/2], low nibble = even k, E2M1 codes (bit 3 = sign)
+ *       scales  uint8 E4M3 bits, one per 16 elements along K, stored in 128x4 tiles of
+ *               512 bytes: offset = ((r/128)*ceil(K/64) + c/4)*512 + (r%32)*16 + ((r%128)/32)*4 + c%4
+ *               buffer size = ceil(rows/128)*128 * ceil(K/64)*4 bytes, padding bytes are zero
+ *       pts     float, the per-tensor scale amax / (6 * 448)
+ */
+#ifndef NVFP4_B200_H_
+#define NVFP4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVFP4_ABI_VERSION 1
+
+enum {
+  NVFP4_OK = 0,
+  NVFP4_E_NULL = -1,      /* a required pointer is NULL */
+  NVFP4_E_SHAPE = -2,     /* a dimension is not positive, or not a multiple of what the op needs */
+  NVFP4_E_ALIGN = -3,     /* a pointer or leading dimension breaks the alignment the op needs */
+  NVFP4_E_MODE = -4,      /* unknown mode / flag value */
+  NVFP4_E_LAUNCH = -5,    /* the CUDA runtime refused the launch (see cudaGetLastError) */
+  NVFP4_E_DRIVER = -6,    /* a driver entry point needed for TMA descriptors is missing */
+  NVFP4_E_WORKSPACE = -7, /* workspace too small */
+  NVFP4_E_LIMIT = -8      /* size beyond a stated maximum of the entry point */
+};
+
+/* Rounding of the E2M1 elements. */
+enum { NVFP4_ROUND_NEAREST = 0, NVFP4_ROUND_STOCHASTIC = 1 };
+/* Output element type of the GEMM. */
+enum { NVFP4_OUT_BF16 = 0, NVFP4_OUT_F32 = 1 };
+
+int nvfp4_version(void);
+const char* nvfp4_status_string(int code); /* host string, static storage */
+
+/*
+ * Per-tensor absolute maximum of a bf16 matrix x[rows, cols] (row stride `ld` elements),
+ * max-merged into *amax (fp32).  With zero_first != 0 the word is cleared on the stream first.
+ * rht != 0: the maximum is taken AFTER the 16-point random-sign Hadamard transform of every
+ * 16-element block (signs16: 16 floats of +-1), blocks running along the columns
+ * (transpose == 0) or along the rows (transpose != 0).
+ * Replaces `tf.abs().amax()` of quant_nvfp4 (nvfp4_gemm.py:34-36) and the bf16 amax of
+ * quant_nvfp4_cuda (nvfp4_cuda.py:170).  A tensor sharded over several GPUs calls this on the
+ * local shard, max-reduces the word across ranks, then calls nvfp4_quantize_bf16.
+ */
+int nvfp4_amax_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                    int rht, int transpose, const float* signs16,
+                    float* amax, int zero_first, void* stream);
+
+/*
+ * NVFP4 quantization of a bf16 matrix x[rows, cols] given its per-tensor amax.
+ *   transpose == 0: 16-element blocks run along the columns; the result describes the
+ *                   [rows, cols] operand (contraction dim = cols).
+ *   transpose != 0: blocks run along the rows; the result describes the TRANSPOSED operand
+ *                   [cols, rows] (contraction dim = rows), i.e. what the reference gets from
+ *                   quant(x.t().contiguous()) (nvfp4_gemm.py:55, nvfp4_train.py:53,77).
+ *   mode: NVFP4_ROUND_NEAREST (ties to even) or NVFP4_ROUND_STOCHASTIC (hardware
+ *         cvt.rs with a Philox4x32-10 stream: one call per block, counter = (block index,
+ *         philox_offset), key = philox_seed; block index = out_row * (K/16) + k/16).
+ *   rht != 0: 16-point random-sign Hadamard of every block before scaling (signs16 as above).
+ *   amax: the word nvfp4_amax_bf16 produced (same rht/transpose); the global scale
+ *         pts = max(amax, 1e-12) / 2688 is computed on the device and written to *pts_out.
+ * Outputs: qdata, scales (layouts above; scales padding is zeroed by this call).
+ * Requirements: contraction dim % 16 == 0, the other dim % 2 == 0, x 16-byte aligned,
+ * ld % 8 == 0.
+ * Replaces quant_nvfp4 (nvfp4_gemm.py:30-48), quant_kernel/quant_launch
+ * (nvfp4_cuda.py:52-133) and the to_blocked swizzle that follows it (nvfp4_cuda.py:184-185).
+ */
+int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                        int transpose, int mode, int rht, const float* signs16,
+                        const float* amax, uint64_t philox_seed, uint64_t philox_offset,
+                        uint8_t* qdata, uint8_t* scales, float* pts_out, void* stream);
+
+/*
+ * Block-scaled FP4 GEMM  D[M, N] = (A . sfA) (B . sfB)^T * (*a_pts) * (*b_pts)
+ * with fp32 accumulation on the tcgen05 tensor cores.
+ *   a_q [M, K/2], b_q [N, K/2]: packed E2M1, both K-major; a_sf, b_sf: swizzled E4M3 scales;
+ *   a_pts, b_pts: device floats; d: [M, ldd] bf16 or fp32.
+ *   status: optional device int32; a bounded wait inside the kernel that gives up writes a
+ *   non-zero code there (the call itself still returns NVFP4_OK).
+ * Requirements: K % 32 == 0 (16-byte rows for TMA), a_q/b_q/d 16-byte aligned.
+ * Replaces torchao's _addmm_nvfp4_dispatch -> torch._scaled_mm as called at
+ * nvfp4_gemm.py:57 and nvfp4_cuda.py:193,200.
+ */
+int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
+               const uint8_t* b_q, const uint8_t* b_sf, const float* b_pts,
+               void* d, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t ldd,
+               int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H_ */

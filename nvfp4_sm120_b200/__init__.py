@@ -1,0 +1,8 @@
+"""B200-native (sm_100a) NVFP4 training hot path behind the reference's Python API.
+
+quant_nvfp4 / fp4_matmul / fp4_mm_preqB, FP4Linear (fprop RNE, dgrad SR, wgrad RHT+SR) and the
+NVFP4_AMORTIZE weight-quant cache with mark_step(), all on hand-written CUDA reached through the
+C ABI of libnvfp4_b200.so."""
+from .tensor import NVFP4Tensor, BLK, swizzled_scale_dims            # noqa: F401
+from .quant import (quant_nvfp4, quant_nvfp4_cuda, tensor_amax, hadamard16,      # noqa: F401
+                    F4_MAX, F8E4M3_MAX, E4M3_EPS)

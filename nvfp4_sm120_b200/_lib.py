@@ -1,0 +1,58 @@
+"""ctypes binding of libnvfp4_b200.so (the C ABI declared in include/nvfp4_b200.h).
+
+There is no fallback: if the library is missing or a call fails, an exception says so."""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libnvfp4_b200.so")
+
+OK = 0
+ROUND_NEAREST, ROUND_STOCHASTIC = 0, 1
+OUT_BF16, OUT_F32 = 0, 1
+
+_c = ctypes
+_SIGS = {
+    "nvfp4_version": (_c.c_int, []),
+    "nvfp4_status_string": (_c.c_char_p, [_c.c_int]),
+    "nvfp4_amax_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
+                                   _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "nvfp4_quantize_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
+                                       _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_uint64, _c.c_uint64,
+                                       _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    "nvfp4_gemm": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                              _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
+                              _c.c_void_p, _c.c_void_p]),
+}
+
+_lib = None
+
+
+class NVFP4Error(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded library.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NVFP4Error(
+                f"{LIB_PATH} is missing: build it with `python -m nvfp4_sm120_b200.build` "
+                "(needs nvcc; targets sm_100a).  There is no CPU or library fallback.")
+        handle = _c.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(handle, name)       # AttributeError here = a symbol the header declares is missing
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def exported_symbols():
+    return list(_SIGS)
+
+
+def check(code, what):
+    if code != OK:
+        msg = lib().nvfp4_status_string(code).decode()
+        raise NVFP4Error(f"{what} failed: {msg} (code {code})")

@@ -1,0 +1,364 @@
+// Per-tensor amax and the fused NVFP4 quantizer for B200 (sm_100a).
+//
+// One pass computes, per 16-element block: [random-sign Hadamard] -> block amax -> E4M3 block
+// scale -> E2M1 codes (round-to-nearest-even, or hardware stochastic rounding fed by a Philox
+// stream) -> packed nibbles, and writes the scale byte straight to its place in the 128x4-tiled
+// layout the tcgen05 block-scaled MMA reads.  The arithmetic follows the reference's pure-torch
+// quantizer operation by operation (nvfp4_gemm.py:36-45): true fp32 divisions, no fast-math.
+#include "common.cuh"
+#include "nvfp4_b200.h"
+
+namespace nvfp4 {
+
+// ---------------------------------------------------------------------------------------
+// shared per-block arithmetic
+// ---------------------------------------------------------------------------------------
+struct GlobalScale {
+  float pts;       // amax / 2688
+  float inv_pts;   // 1 / pts
+};
+
+__device__ __forceinline__ GlobalScale global_scale(const float* __restrict__ amax) {
+  GlobalScale g;
+  g.pts = __fdiv_rn(fmaxf(__ldg(amax), kAmaxFloor), kGlobalDiv);
+  g.inv_pts = __fdiv_rn(1.0f, g.pts);
+  return g;
+}
+
+// v[16] (already Hadamard-transformed if wanted) -> 8 bytes of codes (lo, hi) and the E4M3 byte.
+template <bool SR>
+__device__ __forceinline__ void encode_block(const float (&v)[16], const GlobalScale& g,
+                                             uint64_t blk_index, uint64_t seed, uint64_t offset,
+                                             uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float bs = __fdiv_rn(amax, kF4Max);                                   // nvfp4_gemm.py:39
+  const float sbs = fminf(fmaxf(__fdiv_rn(bs, g.pts), kE4M3Eps), kE4M3Max);   // :40
+  sf_byte = f32_to_e4m3(sbs);
+  const float recip = __fdiv_rn(g.inv_pts, e4m3_to_f32(sf_byte));             // :41
+  // the clamp to +-6 of :42 is the saturation of the conversions below
+  if (SR) {
+    const Philox4 r = philox4x32_10((uint32_t)blk_index, (uint32_t)(blk_index >> 32),
+                                    (uint32_t)offset, (uint32_t)(offset >> 32),
+                                    (uint32_t)seed, (uint32_t)(seed >> 32));
+    const uint32_t q0 = e2m1x4_rs(v[0] * recip, v[1] * recip, v[2] * recip, v[3] * recip, r.x);
+    const uint32_t q1 = e2m1x4_rs(v[4] * recip, v[5] * recip, v[6] * recip, v[7] * recip, r.y);
+    const uint32_t q2 = e2m1x4_rs(v[8] * recip, v[9] * recip, v[10] * recip, v[11] * recip, r.z);
+    const uint32_t q3 = e2m1x4_rs(v[12] * recip, v[13] * recip, v[14] * recip, v[15] * recip, r.w);
+    lo = q0 | (q1 << 16);
+    hi = q2 | (q3 << 16);
+  } else {
+    lo = e2m1x2_rn(v[0] * recip, v[1] * recip) | (e2m1x2_rn(v[2] * recip, v[3] * recip) << 8) |
+         (e2m1x2_rn(v[4] * recip, v[5] * recip) << 16) | (e2m1x2_rn(v[6] * recip, v[7] * recip) << 24);
+    hi = e2m1x2_rn(v[8] * recip, v[9] * recip) | (e2m1x2_rn(v[10] * recip, v[11] * recip) << 8) |
+         (e2m1x2_rn(v[12] * recip, v[13] * recip) << 16) | (e2m1x2_rn(v[14] * recip, v[15] * recip) << 24);
+  }
+}
+
+__device__ __forceinline__ void load_signs(const float* __restrict__ signs16, float (&sg)[16]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 s = __ldg(reinterpret_cast<const float4*>(signs16) + i);
+    sg[4 * i] = s.x; sg[4 * i + 1] = s.y; sg[4 * i + 2] = s.z; sg[4 * i + 3] = s.w;
+  }
+}
+
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
+  // non-negative floats order like their bit patterns
+  atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---------------------------------------------------------------------------------------
+// amax kernels
+// ---------------------------------------------------------------------------------------
+// plain |x| maximum: 16-byte loads, max taken on the bf16 bit patterns (sign cleared)
+__global__ void __launch_bounds__(512) amax_plain_kernel(const uint16_t* __restrict__ x, int64_t rows,
+                                                         int vec_per_row, int64_t ld,
+                                                         float* __restrict__ amax) {
+  const int64_t total = rows * vec_per_row;
+  uint32_t m = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / vec_per_row;
+    const int cv = (int)(i - r * vec_per_row);
+    const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + r * ld) + cv);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      m = max(m, w[j] & 0x7fffu);
+      m = max(m, (w[j] >> 16) & 0x7fffu);
+    }
+  }
+  float f = warp_max(__uint_as_float(m << 16));
+  if ((threadIdx.x & 31) == 0) atomic_max_nonneg(amax, f);
+}
+
+// maximum after the Hadamard transform, blocks along the columns: one thread per block
+__global__ void __launch_bounds__(256) amax_rht_rows_kernel(const uint16_t* __restrict__ x,
+                                                            int64_t rows, int blk_per_row, int64_t ld,
+                                                            const float* __restrict__ signs16,
+                                                            float* __restrict__ amax) {
+  float sg[16];
+  load_signs(signs16, sg);
+  const int64_t total = rows * blk_per_row;
+  float m = 0.0f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / blk_per_row;
+    const int kb = (int)(i - r * blk_per_row);
+    const uint4* p = reinterpret_cast<const uint4*>(x + r * ld + (int64_t)kb * 16);
+    const uint4 a = __ldg(p), b = __ldg(p + 1);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[2 * j] = bf16_lo(w[j]) * sg[2 * j];
+      v[2 * j + 1] = bf16_hi(w[j]) * sg[2 * j + 1];
+    }
+    hadamard16_inplace(v);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) m = fmaxf(m, fabsf(v[j]));
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) atomic_max_nonneg(amax, m);
+}
+
+// ---------------------------------------------------------------------------------------
+// quantizer, blocks along the columns (output describes x itself)
+// ---------------------------------------------------------------------------------------
+template <bool SR, bool RHT>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* __restrict__ x, int64_t rows,
+                                                         int blk_per_row, int64_t ld,
+                                                         const float* __restrict__ signs16,
+                                                         const float* __restrict__ amax,
+                                                         uint64_t seed, uint64_t offset,
+                                                         uint8_t* __restrict__ qdata,
+                                                         uint8_t* __restrict__ scales,
+                                                         float* __restrict__ pts_out) {
+  const GlobalScale g = global_scale(amax);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
+  float sg[16];
+  if (RHT) load_signs(signs16, sg);
+  const int64_t total = rows * blk_per_row;
+  const int64_t col_tiles = (blk_per_row + 3) >> 2;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / blk_per_row;
+    const int kb = (int)(i - r * blk_per_row);
+    const uint4* p = reinterpret_cast<const uint4*>(x + r * ld + (int64_t)kb * 16);
+    const uint4 a = __ldg(p), b = __ldg(p + 1);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[2 * j] = bf16_lo(w[j]);
+      v[2 * j + 1] = bf16_hi(w[j]);
+    }
+    if (RHT) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] *= sg[j];
+      hadamard16_inplace(v);
+    }
+    uint32_t lo, hi, sf;
+    encode_block<SR>(v, g, (uint64_t)i, seed, offset, lo, hi, sf);
+    *reinterpret_cast<uint2*>(qdata + i * 8) = make_uint2(lo, hi);
+    scales[sf_offset(r, kb, col_tiles)] = (uint8_t)sf;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// transposing variants: blocks along the ROWS of x; the output describes x^T [cols, rows].
+// A thread owns two adjacent columns and up to 64 consecutive rows (four 16-row blocks), so
+// that a warp reads 128 contiguous bytes per row and each thread writes 32 contiguous output
+// bytes per column.
+// ---------------------------------------------------------------------------------------
+template <bool RHT>
+__device__ __forceinline__ void load_col_pair_block(const uint16_t* __restrict__ x, int64_t ld,
+                                                    int64_t r0, int64_t c, const float (&sg)[16],
+                                                    float (&v0)[16], float (&v1)[16]) {
+  const uint32_t* p = reinterpret_cast<const uint32_t*>(x + r0 * ld + c);
+  uint32_t w[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) w[i] = __ldg(p + (size_t)i * (size_t)(ld >> 1));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v0[i] = bf16_lo(w[i]);
+    v1[i] = bf16_hi(w[i]);
+    if (RHT) { v0[i] *= sg[i]; v1[i] *= sg[i]; }
+  }
+  if (RHT) { hadamard16_inplace(v0); hadamard16_inplace(v1); }
+}
+
+__global__ void __launch_bounds__(256) amax_rht_cols_kernel(const uint16_t* __restrict__ x, int64_t rows,
+                                                            int64_t cols, int64_t ld,
+                                                            const float* __restrict__ signs16,
+                                                            float* __restrict__ amax) {
+  float sg[16];
+  load_signs(signs16, sg);
+  const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  const int64_t r_base = (int64_t)blockIdx.y * 64;
+  float m = 0.0f;
+  if (c < cols) {
+#pragma unroll 1
+    for (int j = 0; j < 4; ++j) {
+      const int64_t r0 = r_base + 16 * j;
+      if (r0 >= rows) break;
+      float v0[16], v1[16];
+      load_col_pair_block<true>(x, ld, r0, c, sg, v0, v1);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m = fmaxf(m, fmaxf(fabsf(v0[i]), fabsf(v1[i])));
+    }
+  }
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) atomic_max_nonneg(amax, m);
+}
+
+template <bool SR, bool RHT>
+__global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restrict__ x, int64_t rows,
+                                                         int64_t cols, int64_t ld,
+                                                         const float* __restrict__ signs16,
+                                                         const float* __restrict__ amax,
+                                                         uint64_t seed, uint64_t offset,
+                                                         uint8_t* __restrict__ qdata,
+                                                         uint8_t* __restrict__ scales,
+                                                         float* __restrict__ pts_out) {
+  const GlobalScale g = global_scale(amax);
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
+  float sg[16];
+  if (RHT) load_signs(signs16, sg);
+  const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= cols) return;
+  const int64_t r_base = (int64_t)blockIdx.y * 64;
+  const int64_t blk_per_orow = rows >> 4;            // blocks per OUTPUT row (K = rows)
+  const int64_t col_tiles = (blk_per_orow + 3) >> 2;
+  const int64_t out_ld = rows >> 1;                  // bytes per output row
+  uint32_t q[2][8];
+  uint32_t sfw[2] = {0u, 0u};
+  int nvalid = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int64_t r0 = r_base + 16 * j;
+    if (r0 < rows) {
+      float v0[16], v1[16];
+      load_col_pair_block<RHT>(x, ld, r0, c, sg, v0, v1);
+      const uint64_t kb = (uint64_t)(r0 >> 4);
+      uint32_t sf0, sf1;
+      encode_block<SR>(v0, g, (uint64_t)c * blk_per_orow + kb, seed, offset, q[0][2 * j], q[0][2 * j + 1], sf0);
+      encode_block<SR>(v1, g, (uint64_t)(c + 1) * blk_per_orow + kb, seed, offset, q[1][2 * j], q[1][2 * j + 1], sf1);
+      sfw[0] |= sf0 << (8 * j);
+      sfw[1] |= sf1 << (8 * j);
+      nvalid = j + 1;
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    uint8_t* orow = qdata + (c + h) * out_ld + (r_base >> 1);
+    const size_t so = sf_offset(c + h, r_base >> 4, col_tiles);
+    if (nvalid == 4 && (out_ld & 15) == 0) {
+      reinterpret_cast<uint4*>(orow)[0] = make_uint4(q[h][0], q[h][1], q[h][2], q[h][3]);
+      reinterpret_cast<uint4*>(orow)[1] = make_uint4(q[h][4], q[h][5], q[h][6], q[h][7]);
+      *reinterpret_cast<uint32_t*>(scales + so) = sfw[h];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (j < nvalid) {
+          *reinterpret_cast<uint2*>(orow + 8 * j) = make_uint2(q[h][2 * j], q[h][2 * j + 1]);
+          scales[so + j] = (uint8_t)(sfw[h] >> (8 * j));
+        }
+      }
+    }
+  }
+}
+
+static inline int grid_for(int64_t work_items, int threads, int max_blocks) {
+  int64_t b = (work_items + threads - 1) / threads;
+  if (b > max_blocks) b = max_blocks;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+}  // namespace nvfp4
+
+using namespace nvfp4;
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+extern "C" int nvfp4_amax_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int rht,
+                               int transpose, const float* signs16, float* amax, int zero_first,
+                               void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (x == nullptr || amax == nullptr || (rht && signs16 == nullptr)) return NVFP4_E_NULL;
+  if (rows <= 0 || cols <= 0 || ld < cols) return NVFP4_E_SHAPE;
+  if (!aligned16(x) || (ld & 7) != 0 || (rht && !aligned16(signs16))) return NVFP4_E_ALIGN;
+  if (zero_first && cudaMemsetAsync(amax, 0, sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  if (!rht) {
+    if ((cols & 7) != 0) return NVFP4_E_SHAPE;
+    const int vpr = (int)(cols >> 3);
+    amax_plain_kernel<<<grid_for(rows * vpr, 512 * 4, 148 * 8), 512, 0, stream>>>(xp, rows, vpr, ld, amax);
+  } else if (!transpose) {
+    if ((cols & 15) != 0) return NVFP4_E_SHAPE;
+    const int bpr = (int)(cols >> 4);
+    amax_rht_rows_kernel<<<grid_for(rows * bpr, 256 * 2, 148 * 16), 256, 0, stream>>>(xp, rows, bpr, ld, signs16, amax);
+  } else {
+    if ((rows & 15) != 0 || (cols & 1) != 0) return NVFP4_E_SHAPE;
+    dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
+    if (grid.y > 65535u) return NVFP4_E_SHAPE;
+    amax_rht_cols_kernel<<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax);
+  }
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+
+extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
+                                   int mode, int rht, const float* signs16, const float* amax,
+                                   uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
+                                   float* pts_out, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (x == nullptr || amax == nullptr || qdata == nullptr || scales == nullptr || (rht && signs16 == nullptr))
+    return NVFP4_E_NULL;
+  if (rows <= 0 || cols <= 0 || ld < cols) return NVFP4_E_SHAPE;
+  if (mode != NVFP4_ROUND_NEAREST && mode != NVFP4_ROUND_STOCHASTIC) return NVFP4_E_MODE;
+  if (!aligned16(x) || (ld & 7) != 0 || (reinterpret_cast<uintptr_t>(qdata) & 15u) != 0 ||
+      (reinterpret_cast<uintptr_t>(scales) & 15u) != 0 || (rht && !aligned16(signs16)))
+    return NVFP4_E_ALIGN;
+  const int64_t out_rows = transpose ? cols : rows;
+  const int64_t k = transpose ? rows : cols;
+  if ((k & 15) != 0) return NVFP4_E_SHAPE;
+  if (transpose && (cols & 1) != 0) return NVFP4_E_SHAPE;
+  // padding of the tiled scale buffer must read as zero (the reference pads with zeros)
+  const int64_t sm = (out_rows + 127) / 128 * 128, sk = (k / 16 + 3) / 4 * 4;
+  if (sm != out_rows || sk != k / 16) {
+    if (cudaMemsetAsync(scales, 0, (size_t)(sm * sk), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
+  }
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  const bool sr = mode == NVFP4_ROUND_STOCHASTIC;
+  if (!transpose) {
+    const int bpr = (int)(cols >> 4);
+    const int grid = grid_for(rows * bpr, 256, 1 << 30);
+#define NVFP4_LAUNCH_ROWS(SR_, RHT_) \
+    quant_rows_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, bpr, ld, signs16, amax, seed, offset, qdata, scales, pts_out)
+    if (sr && rht) NVFP4_LAUNCH_ROWS(true, true);
+    else if (sr) NVFP4_LAUNCH_ROWS(true, false);
+    else if (rht) NVFP4_LAUNCH_ROWS(false, true);
+    else NVFP4_LAUNCH_ROWS(false, false);
+#undef NVFP4_LAUNCH_ROWS
+  } else {
+    dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
+    if (grid.y > 65535u) return NVFP4_E_SHAPE;
+#define NVFP4_LAUNCH_COLS(SR_, RHT_) \
+    quant_cols_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax, seed, offset, qdata, scales, pts_out)
+    if (sr && rht) NVFP4_LAUNCH_COLS(true, true);
+    else if (sr) NVFP4_LAUNCH_COLS(true, false);
+    else if (rht) NVFP4_LAUNCH_COLS(false, true);
+    else NVFP4_LAUNCH_COLS(false, false);
+#undef NVFP4_LAUNCH_COLS
+  }
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}

@@ -1,0 +1,116 @@
+"""NVFP4 quantizer: the reference's `quant_nvfp4` / `quant_nvfp4_cuda` surface
+(nvfp4_gemm.py:30-48, nvfp4_cuda.py:158-187) on top of the sm_100a kernels."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from .tensor import BLK, NVFP4Tensor, swizzled_scale_dims
+
+F4_MAX, F8E4M3_MAX, E4M3_EPS = 6.0, 448.0, 0.015625
+
+_SEED = [0]          # auto-advancing seed of stochastic calls, like nvfp4_cuda.py:154,160-162
+_H_OK = {}           # H tensors already checked to be the Sylvester matrix / 4
+_ONES = {}
+
+
+def hadamard16(device="cuda"):
+    """Sylvester Hadamard matrix of order 16, divided by 4 (nvfp4_gemm.py:23-27).  The kernels
+    apply exactly this transform as an in-register butterfly; the matrix exists for callers
+    that pass it around."""
+    h = torch.ones(1, 1, device=device, dtype=torch.float32)
+    while h.shape[0] < BLK:
+        h = torch.cat([torch.cat([h, h], 1), torch.cat([h, -h], 1)], 0)
+    return h / math.sqrt(BLK)
+
+
+def _check_h(H):
+    if H is None:
+        return
+    key = (H.data_ptr(), H._version, H.device)
+    if key not in _H_OK:
+        if H.shape != (BLK, BLK) or not torch.equal(H.float().cpu(), hadamard16("cpu")):
+            raise ValueError("H must be hadamard16(): the kernels implement the 16-point Sylvester "
+                             "Hadamard transform only")
+        _H_OK[key] = True
+
+
+def _signs(signs, device):
+    if signs is None:
+        if device not in _ONES:
+            _ONES[device] = torch.ones(BLK, device=device, dtype=torch.float32)
+        return _ONES[device]
+    s = signs.to(device=device, dtype=torch.float32).contiguous()
+    if s.numel() != BLK:
+        raise ValueError("signs must have 16 entries")
+    return s
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _as_bf16_rows(t):
+    if t.dim() != 2:
+        raise ValueError("expected a 2-D tensor")
+    if not t.is_cuda:
+        raise _lib.NVFP4Error("the NVFP4 quantizer runs on a CUDA device only (no CPU path)")
+    x = t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16)
+    if x.stride(1) != 1 or x.stride(0) % 8 != 0 or x.stride(0) < x.shape[1] or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    return x
+
+
+def tensor_amax(t, rht=False, signs=None, transpose=False, out=None):
+    """Per-tensor |x| maximum of a 2-D tensor as a 1-element fp32 CUDA tensor (after the Hadamard
+    transform of its 16-blocks when rht).  No host synchronisation."""
+    x = _as_bf16_rows(t)
+    amax = out if out is not None else torch.empty(1, device=x.device, dtype=torch.float32)
+    sg = _signs(signs, x.device) if rht else None
+    code = _lib.lib().nvfp4_amax_bf16(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), int(rht),
+                                      int(transpose), sg.data_ptr() if rht else None,
+                                      amax.data_ptr(), 1, _stream())
+    _lib.check(code, "nvfp4_amax_bf16")
+    return amax
+
+
+def quant_nvfp4(t, stochastic=False, rht=False, H=None, signs=None, seed=None, *,
+                transpose=False, amax=None, philox_offset=0):
+    """t: [M, K] -> NVFP4Tensor blocked along K (K % 16 == 0), as nvfp4_gemm.py:30-48.
+
+    transpose=True quantizes t.t() (blocks along the rows of t) without materialising the
+    transpose: the result equals quant_nvfp4(t.t().contiguous(), ...).
+    amax: optional 1-element fp32 CUDA tensor to use instead of computing the per-tensor
+    maximum here (a tensor sharded across GPUs passes the all-reduced maximum).
+    seed=None takes the module counter and advances it on stochastic calls."""
+    if seed is None:
+        seed = _SEED[0]
+        if stochastic:
+            _SEED[0] += 1
+    _check_h(H)
+    x = _as_bf16_rows(t)
+    rows, cols = x.shape
+    m, k = (cols, rows) if transpose else (rows, cols)
+    if k % BLK != 0:
+        raise AssertionError(f"K={k} must be divisible by {BLK}")
+    dev = x.device
+    sg = _signs(signs, dev) if rht else None
+    if amax is None:
+        amax = tensor_amax(x, rht, sg, transpose)
+    sm, sk = swizzled_scale_dims(m, k)
+    qdata = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
+    scale = torch.empty((sm, sk), dtype=torch.uint8, device=dev)
+    pts = torch.empty((), dtype=torch.float32, device=dev)
+    code = _lib.lib().nvfp4_quantize_bf16(
+        x.data_ptr(), rows, cols, x.stride(0), int(transpose),
+        _lib.ROUND_STOCHASTIC if stochastic else _lib.ROUND_NEAREST, int(rht),
+        sg.data_ptr() if rht else None, amax.data_ptr(), int(seed) & (2 ** 64 - 1), int(philox_offset),
+        qdata.data_ptr(), scale.data_ptr(), pts.data_ptr(), _stream())
+    _lib.check(code, "nvfp4_quantize_bf16")
+    return NVFP4Tensor(qdata, scale.view(torch.float8_e4m3fn), BLK, t.dtype, pts, True)
+
+
+# the reference's second name for the same entry (nvfp4_cuda.py:158)
+quant_nvfp4_cuda = quant_nvfp4
