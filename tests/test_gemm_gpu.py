@@ -1,0 +1,112 @@
+"""The tcgen05 block-scaled GEMM against the fp32 matmul of the dequantised operands (the oracle)."""
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-3        # BASELINE: within 1e-3 relative error of an fp32 matmul of the dequantised operands
+
+
+@pytest.fixture(scope="module")
+def Q():
+    import nvfp4_sm120_b200 as pkg
+    return pkg
+
+
+def _ref_from_gpu_quant(qa, qb, m, n, k):
+    a = O.dequant_parts(qa.qdata, qa.scale.view(torch.uint8), qa.per_tensor_scale, m, k)
+    b = O.dequant_parts(qb.qdata, qb.scale.view(torch.uint8), qb.per_tensor_scale, n, k)
+    return (a.double() @ b.double().t()).float()
+
+
+@pytest.mark.parametrize("mnk", [(128, 256, 256), (128, 256, 1024), (256, 512, 512), (384, 768, 2048),
+                                 (130, 200, 320), (48, 80, 64), (1024, 1024, 4096), (128, 256, 96)])
+def test_gemm_fp32_out_matches_dequant_matmul(Q, mnk):
+    m, n, k = mnk
+    A = O.synthetic_tensor(m, k, 2)
+    Bt = O.synthetic_tensor(n, k, 3)
+    qa, qb = Q.quant_nvfp4(A.cuda()), Q.quant_nvfp4(Bt.cuda())
+    got = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.float32).cpu()
+    assert Q.gemm_status() == 0
+    ref = _ref_from_gpu_quant(qa, qb, m, n, k)
+    rel = ((got - ref).norm() / ref.norm()).item()
+    assert rel < REL_TOL, f"{mnk}: rel {rel}"
+    assert torch.allclose(got, ref, rtol=2e-3, atol=2e-3 * ref.abs().max().item())
+
+
+def test_gemm_bf16_out_is_rounded_fp32(Q):
+    m, n, k = 256, 512, 1024
+    qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 4).cuda())
+    qb = Q.quant_nvfp4(O.synthetic_tensor(n, k, 5).cuda())
+    f32 = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.float32)
+    bf = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.bfloat16)
+    assert torch.equal(bf, f32.to(torch.bfloat16))
+
+
+def test_config1_end_to_end(Q):
+    """BASELINE config 1 through fp4_matmul: A 2048x4096, B 4096x1024 (outliers x50)."""
+    A = O.synthetic_tensor(2048, 4096, 0)
+    B = O.synthetic_tensor(4096, 1024, 100)
+    got = Q.fp4_matmul(A.cuda(), B.cuda(), out_dtype=torch.float32).cpu()
+    ref = O.fp4_matmul_ref(A, B)
+    rel = ((got - ref).norm() / ref.norm()).item()
+    assert rel < REL_TOL
+    exact = A.float() @ B.float()
+    q_err = ((got - exact).norm() / exact.norm()).item()
+    assert 0.05 < q_err < 0.2          # the quantisation error itself (~0.1 on this input)
+
+
+def test_fp4_matmul_rhs_layouts_and_preq(Q):
+    """B given row-major [K, N] or as the .t() view of [N, K] gives the same bytes; fp4_mm_preqB with
+    a cached quant(B.t()) equals fp4_matmul (nvfp4_cuda.py:196-200)."""
+    A = O.synthetic_tensor(256, 512, 6).cuda()
+    W = O.synthetic_tensor(768, 512, 7).cuda()          # [N, K]
+    y1 = Q.fp4_matmul(A, W.t())
+    y2 = Q.fp4_matmul(A, W.t().contiguous())
+    assert torch.equal(y1, y2)
+    wq = Q.quant_nvfp4(W)
+    assert torch.equal(Q.fp4_mm_preqB(A, wq), y1)
+
+
+def test_gemm_rht_cancels(Q):
+    """The same random-sign Hadamard on both operands cancels in the product (nvfp4_train.py:53-54):
+    the error stays at the quantisation level."""
+    A = O.synthetic_tensor(512, 1024, 8, outliers=False).cuda()
+    B = O.synthetic_tensor(1024, 256, 9, outliers=False).cuda()
+    s = O.signs_from_seed(1).cuda()
+    ref = A.float() @ B.float()
+    plain = Q.fp4_matmul(A, B, out_dtype=torch.float32)
+    rht = Q.fp4_matmul(A, B, rht=True, H=Q.hadamard16("cuda"), signs=s, out_dtype=torch.float32)
+    e0 = ((plain - ref).norm() / ref.norm()).item()
+    e1 = ((rht - ref).norm() / ref.norm()).item()
+    assert e1 < 1.3 * e0 and e0 < 0.2
+
+
+def test_gemm_sr_unbiased(Q):
+    """tests/cuda_val.py:19-26: the mean of 32 stochastic products is closer to the exact product
+    than the round-to-nearest one."""
+    m, k, n = 512, 512, 512
+    g = torch.Generator().manual_seed(0)
+    A = torch.randn(m, k, generator=g).to(torch.bfloat16).cuda()
+    B = torch.randn(k, n, generator=g).to(torch.bfloat16).cuda()
+    ref = A.float() @ B.float()
+    rne = ((Q.fp4_matmul(A, B, out_dtype=torch.float32) - ref).norm() / ref.norm()).item()
+    acc = torch.zeros_like(ref)
+    for i in range(32):
+        acc += Q.fp4_matmul(A, B, sr_a=True, sr_b=True, seed=100 + i, out_dtype=torch.float32)
+    sr = ((acc / 32 - ref).norm() / ref.norm()).item()
+    assert sr < rne
+    assert 0.08 < rne < 0.2
+
+
+def test_gemm_argument_errors(Q):
+    from nvfp4_sm120_b200 import _lib
+    qa = Q.quant_nvfp4(torch.zeros(128, 64, dtype=torch.bfloat16, device="cuda"))
+    qb = Q.quant_nvfp4(torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda"))
+    with pytest.raises(ValueError):
+        Q.nvfp4_mm(qa, qb.t())                       # contraction mismatch
+    with pytest.raises(ValueError):
+        Q.nvfp4_mm(qa, qa)                           # right operand must be the .t() view
+    assert _lib.lib().nvfp4_gemm(None, None, None, None, None, None, None, 0, 1, 1, 32, 1, None, None) == -1
