@@ -1,0 +1,403 @@
+"""Benchmark of the NVFP4 hot path on B200.
+
+Headline line (one JSON object on stdout, rank 0): the fused quantizer on BASELINE config 2 --
+a bf16 8192 x 4096 tensor (N(0,1) seed 1 + 0.1 % x50 outliers) quantized in three modes per step:
+round-to-nearest, stochastic rounding (Philox seed 7), and stochastic rounding after the 16-point
+random-sign Hadamard (sign seed 3).  metric = algorithmic HBM GB/s, bytes = M*K*(2 + 1/2 + 1/16)
+per mode (the reference's own traffic model, tests/cuda_val.py:31).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-extras]
+
+N > 1 (launched under torchrun) runs N independent replicas: this workload does not shard.
+--impl reference times the CPU restatement of the reference's pure-torch quantizer (the oracle
+port; the reference itself needs torchao and a GPU and cannot be installed offline) on the host
+cores, on a bounded row sample of the same tensor.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS, COLS = 8192, 4096
+BYTES_PER_MODE = ROWS * COLS * 2 + ROWS * COLS // 2 + ROWS * COLS // 16      # 85 983 232
+MODES = ("rne", "sr", "rht_sr")
+N_BUF = 6                                   # 6 x 64 MiB inputs = 384 MiB, three times the 126 MB L2
+SR_SEED, SIGN_SEED, DATA_SEED = 7, 3, 1
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2])); power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def synthetic(rows, cols, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, cols, generator=g)
+    n = x.numel()
+    pos = torch.randperm(n, generator=g)[: n // 1000]
+    x.view(-1)[pos] *= 50.0
+    return x.to(torch.bfloat16)
+
+
+def signs_from_seed(seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, 2, (16,), generator=g).float() * 2 - 1
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's pure-torch quantizer
+# ----------------------------------------------------------------------------------------------
+def cpu_step(O, x, signs, H, step):
+    """One pass of the three modes on the host (the reference's algorithm, nvfp4_gemm.py:30-48)."""
+    g = torch.Generator().manual_seed(SR_SEED + step)
+    O.quant_nvfp4(x)
+    O.quant_nvfp4(x, stochastic=True, u=torch.rand(x.shape, generator=g))
+    O.quant_nvfp4(x, stochastic=True, rht=True, H=H, signs=signs, u=torch.rand(x.shape, generator=g))
+
+
+def cpu_sample_rows(O, x_full, signs, H, budget_s):
+    """Rows of the tensor one CPU step can process in about budget_s seconds."""
+    probe = x_full[:256]
+    t0 = time.perf_counter()
+    cpu_step(O, probe, signs, H, 0)
+    per_row = (time.perf_counter() - t0) / 256
+    rows = int(budget_s / per_row) // 128 * 128
+    return max(128, min(ROWS, rows))
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    from oracle import nvfp4_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x_full = synthetic(ROWS, COLS, DATA_SEED)
+    signs, H = signs_from_seed(SIGN_SEED), O.hadamard16()
+    total_steps = args.steps + args.warmup
+    rows = cpu_sample_rows(O, x_full, signs, H, min(2.0, 150.0 / max(1, total_steps)))
+    x = x_full[:rows].contiguous()
+    for i in range(args.warmup):
+        cpu_step(O, x, signs, H, i)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        cpu_step(O, x, signs, H, args.warmup + i)
+    dt = (time.perf_counter() - t0) / args.steps
+    gbs = 3 * (rows * COLS * (2 + 0.5 + 1 / 16)) / dt / 1e9
+    sample = f"{rows} of {ROWS} rows x {COLS} cols per step, three modes (RNE, SR, RHT+SR)"
+    line = {
+        "impl": "reference", "metric": "quantizer HBM GB/s @8192x4096", "value": gbs, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "quantizer sweep bf16 8192x4096: RNE, SR (Philox seed 7), RHT (sign seed 3)+SR",
+                   "l2": "host run"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def time_events(fn, iters, stream):
+    """fn(i) launched iters times; device time between two events on `stream`, in ms per call."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(iters):
+        fn(i)
+    e1.record(stream)
+    e1.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_gpu_arm(args, rank, world, local_rank):
+    import nvfp4_sm120_b200 as Q
+    from nvfp4_sm120_b200 import _lib
+
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    lib = _lib.lib()
+    stream = torch.cuda.current_stream()
+
+    x_host = synthetic(ROWS, COLS, DATA_SEED + rank)
+    xs = [x_host.to(dev)]
+    for i in range(1, N_BUF):                      # distinct contents per buffer, same distribution
+        xs.append(torch.roll(xs[0], shifts=i * 37, dims=0).contiguous())
+    signs = signs_from_seed(SIGN_SEED).to(dev)
+
+    def quant_mode(x, mode, seed):
+        if mode == "rne":
+            return Q.quant_nvfp4(x)
+        if mode == "sr":
+            return Q.quant_nvfp4(x, stochastic=True, seed=seed)
+        return Q.quant_nvfp4(x, stochastic=True, rht=True, signs=signs, seed=seed)
+
+    def step(i):
+        x = xs[i % N_BUF]
+        return [quant_mode(x, m, SR_SEED) for m in MODES]
+
+    # ---- warm-up, then capture one CUDA graph per input buffer (the step is launch-bound from Python)
+    for i in range(max(3, args.warmup)):
+        step(i)
+    torch.cuda.synchronize()
+    graphs, keep = [], []
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for b in range(N_BUF):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                keep.append(step(b))
+            graphs.append(g)
+    torch.cuda.synchronize()
+    for i in range(max(3, args.warmup)):
+        graphs[i % N_BUF].replay()
+    torch.cuda.synchronize()
+
+    # ---- timed region: K steps, barrier + synchronize on both sides, max over ranks
+    # (the clock sampler runs from here to the end of the per-kernel pass below: the timed region
+    # alone lasts a few milliseconds, shorter than one nvidia-smi sample)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for i in range(200):
+        graphs[i % N_BUF].replay()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = time_events(lambda i: graphs[i % N_BUF].replay(), args.steps, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    value = world * 3 * BYTES_PER_MODE / (ms * 1e-3) / 1e9
+
+    # ---- per-kernel durations (roofline): events around each of the six launches of a step
+    amax_buf = torch.empty(1, device=dev, dtype=torch.float32)
+    from nvfp4_sm120_b200.tensor import swizzled_scale_dims
+    sm, sk = swizzled_scale_dims(ROWS, COLS)
+    qd = torch.empty(ROWS, COLS // 2, dtype=torch.uint8, device=dev)
+    sc = torch.empty(sm, sk, dtype=torch.uint8, device=dev)
+    pts = torch.empty((), dtype=torch.float32, device=dev)
+    sp = torch.cuda.current_stream().cuda_stream
+    iters = max(10, args.steps)
+    kern = {}
+    for mode in MODES:
+        rht, sr = int(mode == "rht_sr"), int(mode != "rne")
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(iters)]
+        for i in range(iters):
+            x = xs[i % N_BUF]
+            ev[i][0].record()
+            lib.nvfp4_amax_bf16(x.data_ptr(), ROWS, COLS, COLS, rht, 0, signs.data_ptr(), amax_buf.data_ptr(), 1, sp)
+            ev[i][1].record()
+            lib.nvfp4_quantize_bf16(x.data_ptr(), ROWS, COLS, COLS, 0, sr, rht, signs.data_ptr(), amax_buf.data_ptr(),
+                                    SR_SEED, 0, qd.data_ptr(), sc.data_ptr(), pts.data_ptr(), sp)
+            ev[i][2].record()
+        torch.cuda.synchronize()
+        t_amax = statistics.mean(e[0].elapsed_time(e[1]) for e in ev[2:])
+        t_quant = statistics.mean(e[1].elapsed_time(e[2]) for e in ev[2:])
+        kern[mode] = {"amax_us": t_amax * 1e3, "quant_us": t_quant * 1e3,
+                      "gbs": BYTES_PER_MODE / ((t_amax + t_quant) * 1e-3) / 1e9}
+    for i in range(400):
+        graphs[i % N_BUF].replay()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
+    t_all = sum(k["amax_us"] + k["quant_us"] for k in kern.values()) * 1e-6
+    achieved = 3 * BYTES_PER_MODE / t_all / 1e9
+
+    # ---- end to end through the public API with HOST buffers (pinned), copies inside the timed region
+    x_pin = x_host.pin_memory()
+    outs_host = [(torch.empty(ROWS, COLS // 2, dtype=torch.uint8).pin_memory(),
+                  torch.empty(sm, sk, dtype=torch.uint8).pin_memory(),
+                  torch.empty((), dtype=torch.float32).pin_memory()) for _ in MODES]
+    x_dev = torch.empty_like(xs[0])
+
+    def e2e_step(i):
+        x_dev.copy_(x_pin, non_blocking=True)
+        for m, (hq, hs, hp) in zip(MODES, outs_host):
+            q = quant_mode(x_dev, m, SR_SEED + i)
+            hq.copy_(q.qdata, non_blocking=True)
+            hs.copy_(q.scale.view(torch.uint8), non_blocking=True)
+            hp.copy_(q.per_tensor_scale, non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e2e_iters = max(5, min(args.steps, 20))
+    e2e_ms = time_events(e2e_step, e2e_iters, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_val = world * 3 * BYTES_PER_MODE / (e2e_ms * 1e-3) / 1e9
+    h2d = ROWS * COLS * 2
+    d2h = 3 * (ROWS * COLS // 2 + sm * sk + 4)
+
+    line = {
+        "metric": "quantizer HBM GB/s @8192x4096", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "quantizer sweep bf16 8192x4096: RNE, SR (Philox seed 7), RHT (sign seed 3)+SR",
+                   "bytes_per_mode": BYTES_PER_MODE, "modes_per_step": 3,
+                   "l2": f"inputs rotate over {N_BUF} tensors of 64 MiB (384 MiB, larger than the 126 MB L2)",
+                   "launch": "one CUDA graph per input tensor, replayed", "multi_gpu": "replicas only"},
+        "clocks": clocks,
+        "gpu_launches": 6 * args.steps,
+        "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms, "note": "pinned host input -> device, three quantizations, results -> pinned host"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "amax + quantize launches of all three modes (algorithmic bytes / summed event time)"},
+        "modes": kern,
+    }
+
+    if rank == 0 and world == 1:
+        from oracle import nvfp4_oracle as O
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        Hc, sg = O.hadamard16(), signs_from_seed(SIGN_SEED)
+        rows = cpu_sample_rows(O, x_host, sg, Hc, 6.0)
+        xc = x_host[:rows].contiguous()
+        cpu_step(O, xc[:128], sg, Hc, 0)
+        best = 1e30
+        for r in range(2):
+            t0 = time.perf_counter()
+            cpu_step(O, xc, sg, Hc, r)
+            best = min(best, time.perf_counter() - t0)
+        line["cpu_baseline"] = {"value": 3 * rows * COLS * (2 + 0.5 + 1 / 16) / best / 1e9, "unit": "GB/s",
+                                "cores": cores, "kind": "port",
+                                "sample": f"{rows} of {ROWS} rows x {COLS} cols, three modes, best of 2"}
+        if not args.no_extras:
+            line["extras"] = extras(Q, dev, bf16_peak, peak_kind)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def extras(Q, dev, bf16_peak, peak_kind):
+    """FP4 GEMM throughput on BASELINE config 3 shapes with bf16 torch.matmul alongside."""
+    out = {"gemm": []}
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for (m, n, k) in [(4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384), (16384, 4096, 14336)]:
+        g = torch.Generator(device=dev).manual_seed(2)
+        A = torch.randn(m, k, device=dev, dtype=torch.bfloat16, generator=g)
+        Bt = torch.randn(n, k, device=dev, dtype=torch.bfloat16, generator=g)
+        qa, qb = Q.quant_nvfp4(A), Q.quant_nvfp4(Bt)
+        d = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        def fp4(_):
+            Q.nvfp4_mm(qa, qb.t(), out=d)
+        def bf16(_):
+            torch.matmul(A, Bt.t(), out=d)
+        res = {}
+        for name, fn in (("fp4", fp4), ("bf16", bf16)):
+            for i in range(3):
+                fn(i)
+            ts = []
+            for i in range(10):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(i); e1.record(); e1.synchronize()
+                ts.append(e0.elapsed_time(e1))
+            res[name] = 2.0 * m * n * k / (statistics.median(ts) * 1e-3) / 1e12
+        out["gemm"].append({"m": m, "n": n, "k": k, "fp4_tflops": res["fp4"], "bf16_tflops": res["bf16"],
+                            "frac_of_4x_bf16_peak": res["fp4"] / (4 * bf16_peak),
+                            "frac_of_9pf_datasheet": res["fp4"] / 9000.0})
+        del A, Bt, qa, qb, d
+    out["gemm_peak_kind"] = f"4 x {peak_kind} bf16 burst ({bf16_peak} TF/s)"
+    out["gemm_status"] = Q.gemm_status()
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=60)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (B200); the CPU arm is --impl reference")
+    run_gpu_arm(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,140 @@
+"""FP4Linear: a linear layer whose three GEMMs run in NVFP4 (nvfp4_train.py:19-88).
+
+  fprop  Y  = X  W^T     X: round-to-nearest, W: round-to-nearest            (contraction K)
+  dgrad  dX = dY W       dY: stochastic rounding, W^T: round-to-nearest      (contraction N)
+  wgrad  dW = dY^T X     both through the 16-point random-sign Hadamard along the token
+                         dimension; dY^T: stochastic rounding, X^T: nearest  (contraction M)
+
+Every transposed operand (W^T, dY^T, X^T) is produced by the transposing quantizer straight from
+the row-major tensor, so no transposed copy is ever written (the reference materialises three:
+nvfp4_gemm.py:55, nvfp4_train.py:53,77).
+
+NVFP4_AMORTIZE=1 (read at import, like nvfp4_train.py:20-21) caches the two weight quantizations
+per optimizer step; mark_step() must be called after every optimizer step or the cache goes stale
+(tests/parity_check.py in the reference shows exactly that behaviour)."""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.nn as nn
+
+from .gemm import nvfp4_mm
+from .quant import hadamard16, quant_nvfp4, tensor_amax
+from .tensor import BLK
+
+_STEP = [0]          # bumped once per optimizer step; the weight-quant cache keys on it
+# The reference also wants NVFP4_CUDA=1 before it amortizes, because only its CUDA backend can;
+# here there is one backend, so NVFP4_AMORTIZE alone decides and NVFP4_CUDA is accepted and ignored.
+_AMORTIZE = os.environ.get("NVFP4_AMORTIZE", "0") == "1"
+
+
+def mark_step():
+    """Invalidate every FP4Linear's cached weight quantization (call after optimizer.step())."""
+    _STEP[0] += 1
+
+
+def set_amortize(flag: bool):
+    """Switch the per-step weight-quant cache on or off after import (tests, benchmarks)."""
+    global _AMORTIZE
+    _AMORTIZE = bool(flag)
+
+
+def _grad_dtype(w):
+    return torch.float32 if w.dtype == torch.float32 else torch.bfloat16
+
+
+class FP4LinearFn(torch.autograd.Function):
+    """x: [*, K], w: [N, K] -> [*, N].  wq_K = quant(w) and wq_N = quant(w.t()) may be passed in
+    pre-computed (the amortized path); amax_reduce, if given, is called on every per-tensor amax
+    word of a tensor that is sharded across ranks before it is used (tensor parallelism)."""
+
+    @staticmethod
+    def forward(ctx, x, w, H, signs, wq_K, wq_N, amax_reduce=None, sharded=(False, False)):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        x_sharded, y_sharded = sharded                 # is the K dim / the N dim split across ranks?
+        xq = _quant(x2, amax_reduce if x_sharded else None)
+        if wq_K is None:
+            wq_K = _quant(w, amax_reduce)
+        y = nvfp4_mm(xq, wq_K.t(), torch.bfloat16)
+        ctx.save_for_backward(x2, w)
+        ctx.H, ctx.signs, ctx.xshape, ctx.wq_N = H, signs, x.shape, wq_N
+        ctx.amax_reduce, ctx.sharded = amax_reduce, sharded
+        return y.reshape(*x.shape[:-1], w.shape[0]).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x2, w = ctx.saved_tensors
+        H, signs, wq_N, red = ctx.H, ctx.signs, ctx.wq_N, ctx.amax_reduce
+        x_sharded, y_sharded = ctx.sharded
+        gy2 = gy.reshape(-1, w.shape[0])
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            # dgrad: dX = dY @ W, contraction over N; dY gets stochastic rounding
+            gq = _quant(gy2, red if y_sharded else None, stochastic=True)
+            if wq_N is None:
+                wq_N = _quant(w, red, transpose=True)
+            dx = nvfp4_mm(gq, wq_N.t(), torch.bfloat16).reshape(ctx.xshape).to(gy.dtype)
+        if ctx.needs_input_grad[1]:
+            # wgrad: dW = dY^T @ X, contraction over tokens; Hadamard on both, SR on the gradient
+            gtq = _quant(gy2, red if y_sharded else None, stochastic=True, rht=True, H=H, signs=signs,
+                         transpose=True)
+            xtq = _quant(x2, red if x_sharded else None, rht=True, H=H, signs=signs, transpose=True)
+            dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
+        return dx, dw, None, None, None, None, None, None
+
+
+def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False):
+    if amax_reduce is None:
+        return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose)
+    amax = tensor_amax(t, rht, signs, transpose)
+    amax_reduce(amax)
+    return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose, amax=amax)
+
+
+class FP4Linear(nn.Module):
+    """Drop-in for nn.Linear(cin, cout, bias=False) with fp32 master weights (nvfp4_train.py:58-80)."""
+
+    def __init__(self, cin, cout, device="cuda"):
+        super().__init__()
+        assert cin % BLK == 0 and cout % BLK == 0
+        self.weight = nn.Parameter(torch.empty(cout, cin, device=device))
+        nn.init.normal_(self.weight, std=0.02)
+        self.register_buffer("H", hadamard16(device))
+        g = torch.Generator().manual_seed(1)
+        self.register_buffer("signs", (torch.randint(0, 2, (BLK,), generator=g).float() * 2 - 1).to(device))
+        self._cache_step = -1
+        self._wq_K = self._wq_N = None
+
+    def _weight_quants(self, amax_reduce=None):
+        if not _AMORTIZE:
+            return None, None
+        step = _STEP[0]
+        if self._cache_step != step:
+            w = self.weight.detach()
+            if amax_reduce is None:
+                amax = tensor_amax(w)                      # one amax serves both layouts
+            else:
+                amax = tensor_amax(w)
+                amax_reduce(amax)
+            self._wq_K = quant_nvfp4(w, amax=amax)                      # [N, K], contraction K (fprop)
+            self._wq_N = quant_nvfp4(w, amax=amax, transpose=True)      # [K, N], contraction N (dgrad)
+            self._cache_step = step
+        return self._wq_K, self._wq_N
+
+    def forward(self, x):
+        wq_K, wq_N = self._weight_quants()
+        return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N)
+
+    def extra_repr(self):
+        return f"in_features={self.weight.shape[1]}, out_features={self.weight.shape[0]}, bias=False, nvfp4"
+
+
+def make_linear(cin, cout, use_fp4, device="cuda"):
+    """nvfp4_train.py:83-88."""
+    if use_fp4:
+        return FP4Linear(cin, cout, device)
+    lin = nn.Linear(cin, cout, bias=False, device=device)
+    nn.init.normal_(lin.weight, std=0.02)
+    return lin

@@ -1,0 +1,62 @@
+"""Small fixed cases of the hot-path kernels, for profilers (ncu) and quick timing.
+
+    python -m nvfp4_sm120_b200.profile_case quant --rows 16384 --cols 8192 --mode rht_sr --iters 3
+    python -m nvfp4_sm120_b200.profile_case gemm --m 4096 --n 4096 --k 4096 --iters 3
+
+Prints the CUDA-event time per iteration.  Inputs are random bf16 from a device generator."""
+import argparse
+
+import torch
+
+import nvfp4_sm120_b200 as Q
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["quant", "gemm"])
+    ap.add_argument("--rows", type=int, default=16384)
+    ap.add_argument("--cols", type=int, default=8192)
+    ap.add_argument("--mode", default="rne", choices=["rne", "sr", "rht_sr"])
+    ap.add_argument("--transpose", action="store_true")
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if a.case == "quant":
+        x = torch.randn(a.rows, a.cols, device=dev, dtype=torch.bfloat16, generator=g)
+        signs = torch.ones(16, device=dev)
+        kw = dict(stochastic=a.mode != "rne", rht=a.mode == "rht_sr", signs=signs, seed=7, transpose=a.transpose)
+        Q.quant_nvfp4(x, **kw)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.iters):
+            Q.quant_nvfp4(x, **kw)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.iters
+        nbytes = a.rows * a.cols * (2 + 0.5 + 1 / 16)
+        print(f"quant {a.rows}x{a.cols} {a.mode} transpose={a.transpose}: {ms * 1e3:.1f} us/iter, "
+              f"{nbytes / ms / 1e6:.0f} GB/s algorithmic")
+    else:
+        A = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16, generator=g)
+        Bt = torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16, generator=g)
+        qa, qb = Q.quant_nvfp4(A), Q.quant_nvfp4(Bt)
+        d = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        Q.nvfp4_mm(qa, qb.t(), out=d)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.iters):
+            Q.nvfp4_mm(qa, qb.t(), out=d)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.iters
+        print(f"gemm {a.m}x{a.n}x{a.k}: {ms * 1e3:.1f} us/iter, {2.0 * a.m * a.n * a.k / ms / 1e9:.0f} TFLOP/s, "
+              f"status {Q.gemm_status()}")
+
+
+if __name__ == "__main__":
+    main()
