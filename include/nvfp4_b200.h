@@ -87,6 +87,27 @@ int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
                         uint8_t* qdata, uint8_t* scales, float* pts_out, void* stream);
 
 /*
+ * The same quantization as nvfp4_amax_bf16 + nvfp4_quantize_bf16(transpose == 0) in ONE launch:
+ * a persistent cooperative kernel finds the per-tensor maximum, crosses a grid-wide barrier and
+ * quantizes, keeping as much of the tensor as fits in shared memory between the two phases so
+ * that HBM is read once.  Bit-identical outputs.  `workspace` is caller scratch of at least
+ * nvfp4_quantize_fused_workspace_bytes() bytes (16-byte aligned) that must be ALL ZERO before
+ * its first use (one cudaMemset after allocating it); every call that ends normally leaves it
+ * all zero again, so it can be reused by the next call without clearing.  int32 word 2 of the
+ * workspace becomes non-zero when a bounded wait inside the kernel gave up (outputs are then
+ * undefined; clear the workspace before using it again).  Calls that share a workspace must not
+ * overlap on the GPU: use one workspace per stream.  Needs rows * cols / 16 < 2^31.
+ * Replaces the whole body of quant_nvfp4_cuda (nvfp4_cuda.py:158-187): amax, pts, quant_launch,
+ * to_blocked.
+ */
+size_t nvfp4_quantize_fused_workspace_bytes(void);
+int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                              int mode, int rht, const float* signs16,
+                              uint64_t philox_seed, uint64_t philox_offset,
+                              uint8_t* qdata, uint8_t* scales, float* pts_out,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * Block-scaled FP4 GEMM  D[M, N] = (A . sfA) (B . sfB)^T * (*a_pts) * (*b_pts)
  * with fp32 accumulation on the tcgen05 tensor cores.
  *   a_q [M, K/2], b_q [N, K/2]: packed E2M1, both K-major; a_sf, b_sf: swizzled E4M3 scales;

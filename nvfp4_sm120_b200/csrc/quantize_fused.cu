@@ -1,0 +1,388 @@
+// Single-launch NVFP4 quantizer for a row-major bf16 matrix, blocks along the columns (sm_100a).
+//
+// One persistent cooperative kernel, one CTA per SM, does what the two-launch path does:
+//   phase 1  every CTA takes a contiguous range of 16-element blocks.  The tail of the range is
+//            pulled into shared memory with bulk async copies (it stays there for phase 2), the
+//            head is streamed with 128-bit loads; both feed the per-tensor |x| maximum (taken
+//            after the Hadamard transform when that is on).
+//   barrier  atomicMax into the workspace word, then a grid-wide arrive/wait on a counter
+//            (bounded: a wait that lasts 2 s records an error in the workspace and returns).
+//   phase 2  pts = amax / 2688 on the device; the blocks are quantized from shared memory
+//            (no second HBM read) and, for the streamed head, from global memory, which the L2
+//            still holds.  E4M3 scale bytes go straight to the 128x4-tiled layout.
+// Arithmetic is the reference's (nvfp4_gemm.py:36-45).  Two exact shortcuts keep the kernel
+// memory-bound: the block scale (amax_b/6)/pts is first formed as one multiply and accepted only
+// when its E4M3 rounding provably equals that of the two true divisions (else those are done),
+// and (1/pts)/scale comes from a 128-entry table built per CTA with true divisions.
+#include "common.cuh"
+#include "nvfp4_b200.h"
+
+namespace nvfp4 {
+namespace fused {
+
+constexpr int kThreads = 1024;
+constexpr int kChunkBytes = 16384;                 // one bulk copy
+constexpr int kMaxChunks = 13;                     // 208 KiB of the range stay in shared memory
+constexpr int kStashBytes = kChunkBytes * kMaxChunks;
+constexpr int kSmemBytes = kStashBytes + 1024;     // + table, barrier, reduction scratch
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+struct Workspace {          // 64 bytes of caller scratch: all zero before the first call; every
+  float amax;               // launch that ends normally leaves it all zero again
+  unsigned int arrived;
+  int error;                // sticky: 1 = the grid barrier gave up, 2 = a bulk copy never landed
+  unsigned int done;
+  int pad[12];
+};
+
+struct FastDiv {            // n / d for 0 <= n < 2^31 and a fixed d, as one mulhi and a shift
+  uint32_t mul, shift, d;
+};
+
+__device__ __forceinline__ uint32_t fast_div(uint32_t n, const FastDiv& f) {
+  return f.d == 1 ? n : (__umulhi(n, f.mul) >> f.shift);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+struct Scale {
+  float pts, inv_pts, c;     // c ~ 1 / (6 pts), only used for the checked shortcut
+};
+
+// E4M3 byte of clamp((amax_b / 6) / pts, 2^-6, 448), exactly as the two divisions give it.
+__device__ __forceinline__ uint32_t block_scale_byte(float amax_b, const Scale& s) {
+  const float t = amax_b * s.c;
+  const float lo = fmaxf(t * 0.99999905f, kE4M3Eps);      // t (1 - 2^-20)
+  const float hi = fmaxf(t * 1.00000095f, kE4M3Eps);      // t (1 + 2^-20)
+  uint16_t both;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(both) : "f"(hi), "f"(lo));
+  const uint32_t b_lo = both & 0xffu, b_hi = both >> 8;
+  if (b_lo == b_hi) return b_lo;       // the exact quotient lies between lo and hi: same byte
+  const float sbs = fminf(fmaxf(__fdiv_rn(__fdiv_rn(amax_b, kF4Max), s.pts), kE4M3Eps), kE4M3Max);
+  return f32_to_e4m3(sbs);
+}
+
+__device__ __forceinline__ float amax_packed8(const uint32_t (&w)[8]) {
+  // max |x| over 16 bf16 values held as 8 packed pairs; bf16 magnitudes order like their bits,
+  // so the maximum is taken per 16-bit half with the three-input SIMD max
+  const uint32_t k = 0x7fff7fffu;
+  const uint32_t a = __vimax3_u16x2(w[0] & k, w[1] & k, w[2] & k);
+  const uint32_t b = __vimax3_u16x2(w[3] & k, w[4] & k, w[5] & k);
+  const uint32_t c = __vimax3_u16x2(w[6] & k, w[7] & k, a);
+  const uint32_t m = __vimax3_u16x2(b, c, 0u);
+  return __uint_as_float(max(m << 16, m & 0xffff0000u));
+}
+
+template <bool RHT>
+__device__ __forceinline__ void expand(const uint32_t (&w)[8], const float* sg, float (&v)[16]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (RHT) {
+      // x * sign + 0: an exact zero enters the butterfly as +0, so every exact zero that
+      // leaves it is +0 too, like the output of the reference's matmul with H
+      v[2 * j] = __fmaf_rn(bf16_lo(w[j]), sg[2 * j], 0.0f);
+      v[2 * j + 1] = __fmaf_rn(bf16_hi(w[j]), sg[2 * j + 1], 0.0f);
+    } else {
+      v[2 * j] = bf16_lo(w[j]);
+      v[2 * j + 1] = bf16_hi(w[j]);
+    }
+  }
+  if (RHT) {
+#pragma unroll
+    for (int s = 1; s < 16; s <<= 1) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if ((i & s) == 0) {
+          const float a = v[i], b = v[i | s];
+          v[i] = a + b;
+          v[i | s] = a - b;
+        }
+      }
+    }
+  }
+}
+
+template <bool SR, bool RHT>
+__global__ void __launch_bounds__(kThreads, 1)
+quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_per_row, int64_t ld,
+                   FastDiv div_bpr, const float* __restrict__ signs16, uint64_t seed, uint64_t offset,
+                   uint8_t* __restrict__ qdata, uint8_t* __restrict__ scales, float* __restrict__ pts_out,
+                   Workspace* __restrict__ ws, uint32_t blocks_per_cta, int contiguous) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  float* recip_tab = reinterpret_cast<float*>(smem + kStashBytes);            // 128 floats
+  float* red = reinterpret_cast<float*>(smem + kStashBytes + 512);            // 32 floats
+  float* sgs = reinterpret_cast<float*>(smem + kStashBytes + 640);            // 16 floats
+  const uint32_t bar = smem_u32(smem + kStashBytes + 704);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + kStashBytes + 712);
+
+  const uint32_t total = rows * blk_per_row;
+  const uint32_t b0 = min(total, blockIdx.x * blocks_per_cta);
+  const uint32_t b1 = min(total, b0 + blocks_per_cta);
+  // tail of the range that lives in shared memory (contiguous inputs only)
+  uint32_t stash_blocks = contiguous ? min(b1 - b0, (uint32_t)(kStashBytes / 32)) : 0u;
+  const uint32_t s0 = b1 - stash_blocks;                                      // first stashed block
+  const uint32_t tid = threadIdx.x;
+
+  if (tid == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    *cta_abort = 0;
+    if (stash_blocks > 0) {
+      const uint32_t bytes = stash_blocks * 32u;
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(x) + (size_t)s0 * 32;
+      for (uint32_t o = 0; o < bytes; o += kChunkBytes) {
+        const uint32_t n = min((uint32_t)kChunkBytes, bytes - o);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(smem_u32(smem + o)), "l"(src + o), "r"(n), "r"(bar) : "memory");
+      }
+    }
+  }
+  if (RHT && tid < 16) sgs[tid] = __ldg(signs16 + tid);
+  __syncthreads();
+  float sg[16];
+  if (RHT) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sg[i] = sgs[i];
+  }
+
+  // ------------------------------- phase 1: per-tensor maximum -------------------------------
+  float m = 0.0f;
+  auto load_global = [&](uint32_t i, uint32_t (&w)[8]) {
+    const uint32_t r = fast_div(i, div_bpr);
+    const uint32_t kb = i - r * blk_per_row;
+    const uint4* p = reinterpret_cast<const uint4*>(x + (int64_t)r * ld + (int64_t)kb * 16);
+    const uint4 a = __ldg(p), b = __ldg(p + 1);
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  };
+  auto load_stash = [&](uint32_t i, uint32_t (&w)[8]) {
+    const uint4* p = reinterpret_cast<const uint4*>(smem + (size_t)(i - s0) * 32);
+    const uint4 a = p[0], b = p[1];
+    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  };
+  auto block_max = [&](const uint32_t (&w)[8]) {
+    if (RHT) {
+      float v[16];
+      expand<true>(w, sg, v);
+      float a = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(v[j]));
+      return a * 0.25f;
+    }
+    return amax_packed8(w);
+  };
+#pragma unroll 2
+  for (uint32_t i = b0 + tid; i < s0; i += kThreads) {
+    uint32_t w[8];
+    load_global(i, w);
+    m = fmaxf(m, block_max(w));
+  }
+  if (stash_blocks > 0) {
+    bool landed = mbar_try_wait(bar, 0);
+    if (!landed) {
+      const unsigned long long t0 = global_ns();
+      while (!(landed = mbar_try_wait(bar, 0))) {
+        if (global_ns() - t0 > kWaitLimitNs) break;
+      }
+    }
+    if (!landed) { *cta_abort = 1; ws->error = 2; }
+    for (uint32_t i = s0 + tid; i < b1; i += kThreads) {
+      uint32_t w[8];
+      load_stash(i, w);
+      m = fmaxf(m, block_max(w));
+    }
+  }
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 8));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 4));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+  m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+  if ((tid & 31) == 0) red[tid >> 5] = m;
+  __syncthreads();
+
+  // ------------------------------- grid barrier -------------------------------
+  if (tid < 32) {
+    float mm = red[tid];
+    mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 16));
+    mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 8));
+    mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 4));
+    mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 2));
+    mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 1));
+    if (tid == 0) {
+      atomicMax(reinterpret_cast<unsigned int*>(&ws->amax), __float_as_uint(mm));
+      __threadfence();
+      atomicAdd(&ws->arrived, 1u);
+      const unsigned long long t0 = global_ns();
+      unsigned int seen;
+      uint32_t spins = 0;
+      do {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&ws->arrived) : "memory");
+        if (seen >= gridDim.x) break;
+        if ((++spins & 63u) == 0u && global_ns() - t0 > kWaitLimitNs) { *cta_abort = 1; ws->error = 1; break; }
+      } while (true);
+    }
+  }
+  __syncthreads();
+  if (*cta_abort != 0) return;
+
+  // ------------------------------- phase 2: quantize -------------------------------
+  Scale sc;
+  {
+    float amax;
+    asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(amax) : "l"(&ws->amax) : "memory");
+    sc.pts = __fdiv_rn(fmaxf(amax, kAmaxFloor), kGlobalDiv);
+    sc.inv_pts = __fdiv_rn(1.0f, sc.pts);
+    sc.c = __fdiv_rn(1.0f, kF4Max * sc.pts);
+  }
+  if (blockIdx.x == 0 && tid == 0 && pts_out != nullptr) *pts_out = sc.pts;
+  if (tid < 128) recip_tab[tid] = __fdiv_rn(sc.inv_pts, e4m3_to_f32(tid));
+  __syncthreads();
+  const uint32_t col_tiles = (blk_per_row + 3) >> 2;
+
+  auto quantize = [&](uint32_t i, const uint32_t (&w)[8]) {
+    float v[16];
+    float amax_b;
+    if (RHT) {
+      expand<true>(w, sg, v);
+      amax_b = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) amax_b = fmaxf(amax_b, fabsf(v[j]));
+      amax_b *= 0.25f;                                   // H = butterfly / 4, an exact scaling
+    } else {
+      expand<false>(w, sg, v);
+      amax_b = amax_packed8(w);
+    }
+    const uint32_t sf = block_scale_byte(amax_b, sc);
+    const float recip = RHT ? recip_tab[sf] * 0.25f : recip_tab[sf];
+    uint32_t lo, hi;
+    if (SR) {
+      const uint64_t ctr = (uint64_t)i;
+      const Philox4 r = philox4x32_10((uint32_t)ctr, 0u, (uint32_t)offset, (uint32_t)(offset >> 32),
+                                      (uint32_t)seed, (uint32_t)(seed >> 32));
+      lo = e2m1x4_rs(v[0] * recip, v[1] * recip, v[2] * recip, v[3] * recip, r.x) |
+           (e2m1x4_rs(v[4] * recip, v[5] * recip, v[6] * recip, v[7] * recip, r.y) << 16);
+      hi = e2m1x4_rs(v[8] * recip, v[9] * recip, v[10] * recip, v[11] * recip, r.z) |
+           (e2m1x4_rs(v[12] * recip, v[13] * recip, v[14] * recip, v[15] * recip, r.w) << 16);
+    } else {
+      lo = e2m1x2_rn(v[0] * recip, v[1] * recip) | (e2m1x2_rn(v[2] * recip, v[3] * recip) << 8) |
+           (e2m1x2_rn(v[4] * recip, v[5] * recip) << 16) | (e2m1x2_rn(v[6] * recip, v[7] * recip) << 24);
+      hi = e2m1x2_rn(v[8] * recip, v[9] * recip) | (e2m1x2_rn(v[10] * recip, v[11] * recip) << 8) |
+           (e2m1x2_rn(v[12] * recip, v[13] * recip) << 16) | (e2m1x2_rn(v[14] * recip, v[15] * recip) << 24);
+    }
+    const uint32_t r = fast_div(i, div_bpr);
+    const uint32_t kb = i - r * blk_per_row;
+    *reinterpret_cast<uint2*>(qdata + (size_t)i * 8) = make_uint2(lo, hi);
+    const uint32_t tile = (r >> 7) * col_tiles + (kb >> 2);
+    scales[(size_t)tile * 512 + ((r & 31u) << 4) + (((r >> 5) & 3u) << 2) + (kb & 3u)] = (uint8_t)sf;
+  };
+  // stashed tail first (no global read), then the streamed head out of the L2
+  for (uint32_t i = s0 + tid; i < b1; i += kThreads) {
+    uint32_t w[8];
+    load_stash(i, w);
+    quantize(i, w);
+  }
+#pragma unroll 2
+  for (uint32_t i = b0 + tid; i < s0; i += kThreads) {
+    uint32_t w[8];
+    load_global(i, w);
+    quantize(i, w);
+  }
+  // the last CTA to finish puts the workspace back to zero for the next launch
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(&ws->done, 1u) == gridDim.x - 1) {
+      ws->amax = 0.0f;
+      ws->arrived = 0u;
+      ws->done = 0u;
+      __threadfence();
+    }
+  }
+}
+
+static FastDiv make_fast_div(uint32_t d) {
+  // Granlund-Montgomery for 31-bit dividends: with l = ceil(log2 d), mul = ceil(2^(31+l) / d) fits
+  // 32 bits and n / d == mulhi(n, mul) >> (l - 1) for every n < 2^31.
+  FastDiv f{0, 0, d};
+  if (d == 1) return f;
+  uint32_t l = 0;
+  while ((1ull << l) < d) ++l;
+  f.mul = (uint32_t)(((1ull << (31 + l)) + d - 1) / d);
+  f.shift = l - 1;
+  return f;
+}
+
+}  // namespace fused
+}  // namespace nvfp4
+
+using namespace nvfp4;
+using namespace nvfp4::fused;
+
+extern "C" size_t nvfp4_quantize_fused_workspace_bytes(void) { return sizeof(Workspace); }
+
+extern "C" int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode,
+                                         int rht, const float* signs16, uint64_t seed, uint64_t offset,
+                                         uint8_t* qdata, uint8_t* scales, float* pts_out, void* workspace,
+                                         size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!x || !qdata || !scales || !workspace || (rht && !signs16)) return NVFP4_E_NULL;
+  if (workspace_bytes < sizeof(Workspace)) return NVFP4_E_WORKSPACE;
+  if (rows <= 0 || cols <= 0 || ld < cols || (cols & 15) != 0) return NVFP4_E_SHAPE;
+  if (rows * (cols / 16) >= (1ll << 31)) return NVFP4_E_LIMIT;
+  if (mode != NVFP4_ROUND_NEAREST && mode != NVFP4_ROUND_STOCHASTIC) return NVFP4_E_MODE;
+  auto mis = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  if (mis(x, 16) || (ld & 7) != 0 || mis(qdata, 16) || mis(scales, 16) || mis(workspace, 16)) return NVFP4_E_ALIGN;
+
+  static int sm_count[64] = {};
+  static bool attr_done[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
+  if (sm_count[dev] == 0 &&
+      cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return NVFP4_E_LAUNCH;
+  const bool sr = mode == NVFP4_ROUND_STOCHASTIC;
+  const void* fn = sr ? (rht ? (const void*)quant_fused_kernel<true, true> : (const void*)quant_fused_kernel<true, false>)
+                      : (rht ? (const void*)quant_fused_kernel<false, true> : (const void*)quant_fused_kernel<false, false>);
+  if (!attr_done[dev]) {
+    const void* all[4] = {(const void*)quant_fused_kernel<true, true>, (const void*)quant_fused_kernel<true, false>,
+                          (const void*)quant_fused_kernel<false, true>, (const void*)quant_fused_kernel<false, false>};
+    for (const void* f : all)
+      if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+        return NVFP4_E_LAUNCH;
+    attr_done[dev] = true;
+  }
+  const int64_t sm = (rows + 127) / 128 * 128, sk = (cols / 16 + 3) / 4 * 4;
+  if (sm != rows || sk != cols / 16) {
+    if (cudaMemsetAsync(scales, 0, (size_t)(sm * sk), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
+  }
+
+  uint32_t rows32 = (uint32_t)rows, bpr = (uint32_t)(cols / 16);
+  const uint32_t total = rows32 * bpr;
+  uint32_t grid = (uint32_t)sm_count[dev];
+  const uint32_t min_per_cta = 2048;                       // do not spread tiny tensors over all SMs
+  if ((uint64_t)grid * min_per_cta > total) grid = (total + min_per_cta - 1) / min_per_cta;
+  if (grid < 1) grid = 1;
+  uint32_t per = (total + grid - 1) / grid;
+  per = (per + 31u) & ~31u;                                // whole warps of blocks, 1 KiB-aligned ranges
+  FastDiv fd = make_fast_div(bpr);
+  int contiguous = (ld == cols) ? 1 : 0;
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  Workspace* ws = static_cast<Workspace*>(workspace);
+  void* args[] = {&xp, &rows32, &bpr, &ld, &fd, &signs16, &seed, &offset, &qdata, &scales, &pts_out, &ws, &per,
+                  &contiguous};
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, kSmemBytes, stream);
+  return e == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}

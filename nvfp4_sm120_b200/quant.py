@@ -48,6 +48,26 @@ def _signs(signs, device):
     return s
 
 
+_WS = {}
+
+
+def _workspace(device):
+    """Zeroed 64-byte scratch of the single-launch quantizer, one per (device, stream): the kernel
+    leaves it zeroed, and launches on one stream never overlap."""
+    key = (device, torch.cuda.current_stream().cuda_stream)
+    if key not in _WS:
+        _WS[key] = torch.zeros(16, dtype=torch.int32, device=device)
+    return _WS[key]
+
+
+def fused_error(device=None) -> int:
+    """Sticky error word of the single-launch quantizer's workspace on the current stream
+    (0 = none).  Reading it synchronises."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device, torch.cuda.current_stream().cuda_stream)
+    return int(_WS[key][2].item()) if key in _WS else 0
+
+
 def _stream():
     return torch.cuda.current_stream().cuda_stream
 
@@ -77,14 +97,16 @@ def tensor_amax(t, rht=False, signs=None, transpose=False, out=None):
 
 
 def quant_nvfp4(t, stochastic=False, rht=False, H=None, signs=None, seed=None, *,
-                transpose=False, amax=None, philox_offset=0):
+                transpose=False, amax=None, philox_offset=0, fused=True):
     """t: [M, K] -> NVFP4Tensor blocked along K (K % 16 == 0), as nvfp4_gemm.py:30-48.
 
     transpose=True quantizes t.t() (blocks along the rows of t) without materialising the
     transpose: the result equals quant_nvfp4(t.t().contiguous(), ...).
     amax: optional 1-element fp32 CUDA tensor to use instead of computing the per-tensor
     maximum here (a tensor sharded across GPUs passes the all-reduced maximum).
-    seed=None takes the module counter and advances it on stochastic calls."""
+    seed=None takes the module counter and advances it on stochastic calls.
+    fused=False forces the two-launch path (amax kernel, then quantize kernel) where the
+    single-launch cooperative kernel would be used; both give the same bytes."""
     if seed is None:
         seed = _SEED[0]
         if stochastic:
@@ -97,12 +119,21 @@ def quant_nvfp4(t, stochastic=False, rht=False, H=None, signs=None, seed=None, *
         raise AssertionError(f"K={k} must be divisible by {BLK}")
     dev = x.device
     sg = _signs(signs, dev) if rht else None
-    if amax is None:
-        amax = tensor_amax(x, rht, sg, transpose)
     sm, sk = swizzled_scale_dims(m, k)
     qdata = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
     scale = torch.empty((sm, sk), dtype=torch.uint8, device=dev)
     pts = torch.empty((), dtype=torch.float32, device=dev)
+    if fused and amax is None and not transpose and rows * (cols // BLK) < 2 ** 31:
+        ws = _workspace(dev)
+        code = _lib.lib().nvfp4_quantize_fused_bf16(
+            x.data_ptr(), rows, cols, x.stride(0),
+            _lib.ROUND_STOCHASTIC if stochastic else _lib.ROUND_NEAREST, int(rht),
+            sg.data_ptr() if rht else None, int(seed) & (2 ** 64 - 1), int(philox_offset),
+            qdata.data_ptr(), scale.data_ptr(), pts.data_ptr(), ws.data_ptr(), 64, _stream())
+        _lib.check(code, "nvfp4_quantize_fused_bf16")
+        return NVFP4Tensor(qdata, scale.view(torch.float8_e4m3fn), BLK, t.dtype, pts, True)
+    if amax is None:
+        amax = tensor_amax(x, rht, sg, transpose)
     code = _lib.lib().nvfp4_quantize_bf16(
         x.data_ptr(), rows, cols, x.stride(0), int(transpose),
         _lib.ROUND_STOCHASTIC if stochastic else _lib.ROUND_NEAREST, int(rht),

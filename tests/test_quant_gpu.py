@@ -199,3 +199,29 @@ def test_full_size_properties(Q):
     assert torch.equal(qs.scale.view(torch.uint8), sc)
     d = (lv[(qs.qdata & 7).long()] - lv[(q.qdata & 7).long()]).abs()
     assert float(d.max()) <= 2.0 and 0.05 < float((d > 0).float().mean()) < 0.6
+
+
+@pytest.mark.parametrize("shape", [(16, 32), (130, 192), (2048, 4096), (5328, 768), (8192, 4096), (1000, 7168)])
+def test_single_launch_equals_two_launch(Q, shape):
+    """The persistent cooperative kernel and the amax + quantize pair give the same bytes in all
+    three modes, and the cooperative kernel leaves its workspace clean."""
+    from nvfp4_sm120_b200 import quant
+    x = O.synthetic_tensor(shape[0], shape[1], 31).cuda()
+    s = O.signs_from_seed(3).cuda()
+    for kw in (dict(), dict(stochastic=True, seed=9), dict(stochastic=True, rht=True, signs=s, seed=9),
+               dict(rht=True, signs=s)):
+        a = Q.quant_nvfp4(x, fused=True, **kw)
+        b = Q.quant_nvfp4(x, fused=False, **kw)
+        assert torch.equal(a.qdata, b.qdata), kw
+        assert torch.equal(a.scale.view(torch.uint8), b.scale.view(torch.uint8)), kw
+        assert torch.equal(a.per_tensor_scale, b.per_tensor_scale), kw
+    assert quant.fused_error() == 0
+    assert int(quant._workspace(x.device).abs().sum().item()) == 0
+
+
+def test_single_launch_strided_input(Q):
+    big = O.synthetic_tensor(512, 2048, 32).cuda()
+    view = big[:, 512:1536]
+    a = Q.quant_nvfp4(view, fused=True)
+    b = Q.quant_nvfp4(view.contiguous(), fused=False)
+    assert torch.equal(a.qdata, b.qdata) and torch.equal(a.scale.view(torch.uint8), b.scale.view(torch.uint8))
