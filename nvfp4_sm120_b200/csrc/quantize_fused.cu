@@ -26,13 +26,16 @@ constexpr int kMaxChunks = 13;                     // 208 KiB of the range stay 
 constexpr int kStashBytes = kChunkBytes * kMaxChunks;
 constexpr int kSmemBytes = kStashBytes + 1024;     // + table, barrier, reduction scratch
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr int kBatch = 4;                          // blocks per thread in flight, amax pass
+constexpr int kBatch2 = 2;                         // same, quantize pass (register budget: 64)
 
 struct Workspace {          // 64 bytes of caller scratch: all zero before the first call; every
   float amax;               // launch that ends normally leaves it all zero again
   unsigned int arrived;
   int error;                // sticky: 1 = the grid barrier gave up, 2 = a bulk copy never landed
   unsigned int done;
-  int pad[12];
+  unsigned long long stamp[5];   // diagnostics: globaltimer of CTA 0 at start, after the streamed
+  int pad[2];                    // amax, after the stashed amax, after the barrier, at the end
 };
 
 struct FastDiv {            // n / d for 0 <= n < 2^31 and a fixed d, as one mulhi and a shift
@@ -86,31 +89,67 @@ __device__ __forceinline__ float amax_packed8(const uint32_t (&w)[8]) {
   return __uint_as_float(max(m << 16, m & 0xffff0000u));
 }
 
+// ---- packed fp32 helpers (sm_100 has two-wide fp32 add / mul) ----------------------------------
+__device__ __forceinline__ void mul2(float a, float b, float s, float& d0, float& d1) {
+  asm("{.reg .b64 p, q, r; mov.b64 p, {%2, %3}; mov.b64 q, {%4, %4}; mul.rn.f32x2 r, p, q; mov.b64 {%0, %1}, r;}"
+      : "=f"(d0), "=f"(d1) : "f"(a), "f"(b), "f"(s));
+}
+// (a0, a1) and (b0, b1) -> sums into a, differences into b
+__device__ __forceinline__ void addsub2(float& a0, float& a1, float& b0, float& b1) {
+  float s0, s1, d0, d1;
+  asm("{.reg .b64 p, q, r, t; mov.b64 p, {%4, %5}; mov.b64 q, {%6, %7}; add.rn.f32x2 r, p, q; sub.rn.f32x2 t, p, q;"
+      " mov.b64 {%0, %1}, r; mov.b64 {%2, %3}, t;}"
+      : "=f"(s0), "=f"(s1), "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+  a0 = s0; a1 = s1; b0 = d0; b1 = d1;
+}
+// eight fp32 -> eight E2M1 codes in one word, round to nearest even; d[0] in the lowest nibble
+__device__ __forceinline__ uint32_t e2m1x8_rn(const float* d) {
+  uint32_t w;
+  asm("{.reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};}"
+      : "=r"(w) : "f"(d[0]), "f"(d[1]), "f"(d[2]), "f"(d[3]), "f"(d[4]), "f"(d[5]), "f"(d[6]), "f"(d[7]));
+  return w;
+}
+
+struct PhiloxKeys { uint32_t k[10][2]; };     // round keys key + r * (0x9E3779B9, 0xBB67AE85), host-made
+
+__device__ __forceinline__ Philox4 philox_rounds(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                                 const PhiloxKeys& ks) {
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0, p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ ks.k[r][0];
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ ks.k[r][1];
+    c1 = (uint32_t)p1; c3 = (uint32_t)p0; c0 = n0; c2 = n2;
+  }
+  return Philox4{c0, c1, c2, c3};
+}
+
+// 16 bf16 (8 words) -> fp32 v[16].  RHT: signs are applied by flipping sign bits of the packed
+// words, then the 16-point butterfly runs (strides 1, 2, 4, 8; the last three two lanes at a time);
+// the result is 4x the Hadamard transform (the 1/4 is folded into the scale by the caller).
+// A -0 can only leave the butterfly when all 16 inputs are zeros, which the caller handles.
 template <bool RHT>
-__device__ __forceinline__ void expand(const uint32_t (&w)[8], const float* sg, float (&v)[16]) {
+__device__ __forceinline__ void expand(const uint32_t (&w)[8], const uint32_t (&sm)[8], float (&v)[16]) {
+  if constexpr (!RHT) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { v[2 * j] = bf16_lo(w[j]); v[2 * j + 1] = bf16_hi(w[j]); }
+    return;
+  }
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
-    if (RHT) {
-      // x * sign + 0: an exact zero enters the butterfly as +0, so every exact zero that
-      // leaves it is +0 too, like the output of the reference's matmul with H
-      v[2 * j] = __fmaf_rn(bf16_lo(w[j]), sg[2 * j], 0.0f);
-      v[2 * j + 1] = __fmaf_rn(bf16_hi(w[j]), sg[2 * j + 1], 0.0f);
-    } else {
-      v[2 * j] = bf16_lo(w[j]);
-      v[2 * j + 1] = bf16_hi(w[j]);
-    }
+    const uint32_t x = w[j] ^ sm[j];
+    const float lo = bf16_lo(x), hi = bf16_hi(x);
+    v[2 * j] = lo + hi;
+    v[2 * j + 1] = lo - hi;
   }
-  if (RHT) {
 #pragma unroll
-    for (int s = 1; s < 16; s <<= 1) {
+  for (int s = 2; s < 16; s <<= 1) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        if ((i & s) == 0) {
-          const float a = v[i], b = v[i | s];
-          v[i] = a + b;
-          v[i | s] = a - b;
-        }
-      }
+    for (int i = 0; i < 16; i += 2) {
+      if ((i & s) == 0) addsub2(v[i], v[i + 1], v[i | s], v[(i | s) + 1]);
     }
   }
 }
@@ -118,7 +157,7 @@ __device__ __forceinline__ void expand(const uint32_t (&w)[8], const float* sg, 
 template <bool SR, bool RHT>
 __global__ void __launch_bounds__(kThreads, 1)
 quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_per_row, int64_t ld,
-                   FastDiv div_bpr, const float* __restrict__ signs16, uint64_t seed, uint64_t offset,
+                   FastDiv div_bpr, const float* __restrict__ signs16, PhiloxKeys keys, uint64_t offset,
                    uint8_t* __restrict__ qdata, uint8_t* __restrict__ scales, float* __restrict__ pts_out,
                    Workspace* __restrict__ ws, uint32_t blocks_per_cta, int contiguous) {
   extern __shared__ __align__(128) uint8_t smem[];
@@ -152,12 +191,13 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     }
   }
   if (RHT && tid < 16) sgs[tid] = __ldg(signs16 + tid);
+  const bool stamper = blockIdx.x == 0 && tid == 0;
+  if (stamper) ws->stamp[0] = global_ns();
   __syncthreads();
-  float sg[16];
-  if (RHT) {
+  uint32_t sm[8];                 // sign-bit masks of the packed bf16 pairs (bit 15: even, bit 31: odd)
 #pragma unroll
-    for (int i = 0; i < 16; ++i) sg[i] = sgs[i];
-  }
+  for (int j = 0; j < 8; ++j)
+    sm[j] = RHT ? ((sgs[2 * j] < 0.0f ? 0x8000u : 0u) | (sgs[2 * j + 1] < 0.0f ? 0x80000000u : 0u)) : 0u;
 
   // ------------------------------- phase 1: per-tensor maximum -------------------------------
   float m = 0.0f;
@@ -176,7 +216,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   auto block_max = [&](const uint32_t (&w)[8]) {
     if (RHT) {
       float v[16];
-      expand<true>(w, sg, v);
+      expand<true>(w, sm, v);
       float a = 0.0f;
 #pragma unroll
       for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(v[j]));
@@ -184,12 +224,18 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     }
     return amax_packed8(w);
   };
-#pragma unroll 2
-  for (uint32_t i = b0 + tid; i < s0; i += kThreads) {
-    uint32_t w[8];
-    load_global(i, w);
-    m = fmaxf(m, block_max(w));
+  // the streamed head, kBatch blocks per thread in flight before any of them is consumed
+  for (uint32_t i = b0 + tid; i < s0; i += kBatch * kThreads) {
+    uint32_t w[kBatch][8];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const uint32_t iu = min(i + u * kThreads, s0 - 1);     // clamped duplicates cost no extra traffic
+      load_global(iu, w[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) m = fmaxf(m, block_max(w[u]));
   }
+  if (stamper) ws->stamp[1] = global_ns();
   if (stash_blocks > 0) {
     bool landed = mbar_try_wait(bar, 0);
     if (!landed) {
@@ -212,6 +258,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
   if ((tid & 31) == 0) red[tid >> 5] = m;
   __syncthreads();
+  if (stamper) ws->stamp[2] = global_ns();
 
   // ------------------------------- grid barrier -------------------------------
   if (tid < 32) {
@@ -237,6 +284,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   }
   __syncthreads();
   if (*cta_abort != 0) return;
+  if (stamper) ws->stamp[3] = global_ns();
 
   // ------------------------------- phase 2: quantize -------------------------------
   Scale sc;
@@ -256,32 +304,30 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     float v[16];
     float amax_b;
     if (RHT) {
-      expand<true>(w, sg, v);
+      expand<true>(w, sm, v);
       amax_b = 0.0f;
 #pragma unroll
       for (int j = 0; j < 16; ++j) amax_b = fmaxf(amax_b, fabsf(v[j]));
       amax_b *= 0.25f;                                   // H = butterfly / 4, an exact scaling
     } else {
-      expand<false>(w, sg, v);
+      expand<false>(w, sm, v);
       amax_b = amax_packed8(w);
     }
     const uint32_t sf = block_scale_byte(amax_b, sc);
     const float recip = RHT ? recip_tab[sf] * 0.25f : recip_tab[sf];
+    float d[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mul2(v[2 * j], v[2 * j + 1], recip, d[2 * j], d[2 * j + 1]);
     uint32_t lo, hi;
     if (SR) {
-      const uint64_t ctr = (uint64_t)i;
-      const Philox4 r = philox4x32_10((uint32_t)ctr, 0u, (uint32_t)offset, (uint32_t)(offset >> 32),
-                                      (uint32_t)seed, (uint32_t)(seed >> 32));
-      lo = e2m1x4_rs(v[0] * recip, v[1] * recip, v[2] * recip, v[3] * recip, r.x) |
-           (e2m1x4_rs(v[4] * recip, v[5] * recip, v[6] * recip, v[7] * recip, r.y) << 16);
-      hi = e2m1x4_rs(v[8] * recip, v[9] * recip, v[10] * recip, v[11] * recip, r.z) |
-           (e2m1x4_rs(v[12] * recip, v[13] * recip, v[14] * recip, v[15] * recip, r.w) << 16);
+      const Philox4 r = philox_rounds(i, 0u, (uint32_t)offset, (uint32_t)(offset >> 32), keys);
+      lo = e2m1x4_rs(d[0], d[1], d[2], d[3], r.x) | (e2m1x4_rs(d[4], d[5], d[6], d[7], r.y) << 16);
+      hi = e2m1x4_rs(d[8], d[9], d[10], d[11], r.z) | (e2m1x4_rs(d[12], d[13], d[14], d[15], r.w) << 16);
     } else {
-      lo = e2m1x2_rn(v[0] * recip, v[1] * recip) | (e2m1x2_rn(v[2] * recip, v[3] * recip) << 8) |
-           (e2m1x2_rn(v[4] * recip, v[5] * recip) << 16) | (e2m1x2_rn(v[6] * recip, v[7] * recip) << 24);
-      hi = e2m1x2_rn(v[8] * recip, v[9] * recip) | (e2m1x2_rn(v[10] * recip, v[11] * recip) << 8) |
-           (e2m1x2_rn(v[12] * recip, v[13] * recip) << 16) | (e2m1x2_rn(v[14] * recip, v[15] * recip) << 24);
+      lo = e2m1x8_rn(d);
+      hi = e2m1x8_rn(d + 8);
     }
+    if (RHT && amax_b == 0.0f) { lo = 0u; hi = 0u; }     // an all-zero block is +0 everywhere
     const uint32_t r = fast_div(i, div_bpr);
     const uint32_t kb = i - r * blk_per_row;
     *reinterpret_cast<uint2*>(qdata + (size_t)i * 8) = make_uint2(lo, hi);
@@ -294,14 +340,20 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     load_stash(i, w);
     quantize(i, w);
   }
-#pragma unroll 2
-  for (uint32_t i = b0 + tid; i < s0; i += kThreads) {
-    uint32_t w[8];
-    load_global(i, w);
-    quantize(i, w);
+  for (uint32_t i = b0 + tid; i < s0; i += kBatch2 * kThreads) {
+    uint32_t w[kBatch2][8];
+#pragma unroll
+    for (int u = 0; u < kBatch2; ++u) {
+      const uint32_t iu = min(i + u * kThreads, s0 - 1);
+      load_global(iu, w[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch2; ++u)
+      if (i + u * kThreads < s0) quantize(i + u * kThreads, w[u]);
   }
   // the last CTA to finish puts the workspace back to zero for the next launch
   __syncthreads();
+  if (stamper) ws->stamp[4] = global_ns();
   if (tid == 0) {
     __threadfence();
     if (atomicAdd(&ws->done, 1u) == gridDim.x - 1) {
@@ -381,7 +433,12 @@ extern "C" int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t co
   int contiguous = (ld == cols) ? 1 : 0;
   const uint16_t* xp = static_cast<const uint16_t*>(x);
   Workspace* ws = static_cast<Workspace*>(workspace);
-  void* args[] = {&xp, &rows32, &bpr, &ld, &fd, &signs16, &seed, &offset, &qdata, &scales, &pts_out, &ws, &per,
+  PhiloxKeys keys;
+  for (int r = 0; r < 10; ++r) {
+    keys.k[r][0] = (uint32_t)seed + (uint32_t)r * 0x9E3779B9u;
+    keys.k[r][1] = (uint32_t)(seed >> 32) + (uint32_t)r * 0xBB67AE85u;
+  }
+  void* args[] = {&xp, &rows32, &bpr, &ld, &fd, &signs16, &keys, &offset, &qdata, &scales, &pts_out, &ws, &per,
                   &contiguous};
   cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, kSmemBytes, stream);
   return e == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;

@@ -216,7 +216,7 @@ def test_single_launch_equals_two_launch(Q, shape):
         assert torch.equal(a.scale.view(torch.uint8), b.scale.view(torch.uint8)), kw
         assert torch.equal(a.per_tensor_scale, b.per_tensor_scale), kw
     assert quant.fused_error() == 0
-    assert int(quant._workspace(x.device).abs().sum().item()) == 0
+    assert int(quant._workspace(x.device)[:4].abs().sum().item()) == 0      # words 4.. are time stamps
 
 
 def test_single_launch_strided_input(Q):
