@@ -22,9 +22,11 @@ namespace fused {
 
 constexpr int kThreads = 1024;
 constexpr int kChunkBytes = 16384;                 // one bulk copy
-constexpr int kMaxChunks = 13;                     // 208 KiB of the range stay in shared memory
+constexpr int kMaxChunks = 12;                     // 192 KiB of the range stay in shared memory
 constexpr int kStashBytes = kChunkBytes * kMaxChunks;
-constexpr int kSmemBytes = kStashBytes + 1024;     // + table, barrier, reduction scratch
+constexpr int kTabBlocks = 16384;                  // block maxima of phase 1 kept for phase 2 (2 B each)
+constexpr int kMiscOff = kStashBytes + 2 * kTabBlocks;
+constexpr int kSmemBytes = kMiscOff + 1024;        // + reciprocal table, barrier, reduction scratch
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kBatch = 4;                          // blocks per thread in flight, amax pass
 constexpr int kBatch2 = 2;                         // same, quantize pass (register budget: 64)
@@ -161,11 +163,12 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
                    uint8_t* __restrict__ qdata, uint8_t* __restrict__ scales, float* __restrict__ pts_out,
                    Workspace* __restrict__ ws, uint32_t blocks_per_cta, int contiguous) {
   extern __shared__ __align__(128) uint8_t smem[];
-  float* recip_tab = reinterpret_cast<float*>(smem + kStashBytes);            // 128 floats
-  float* red = reinterpret_cast<float*>(smem + kStashBytes + 512);            // 32 floats
-  float* sgs = reinterpret_cast<float*>(smem + kStashBytes + 640);            // 16 floats
-  const uint32_t bar = smem_u32(smem + kStashBytes + 704);
-  volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + kStashBytes + 712);
+  uint16_t* amax_tab = reinterpret_cast<uint16_t*>(smem + kStashBytes);       // bf16 bits, no RHT only
+  float* recip_tab = reinterpret_cast<float*>(smem + kMiscOff);               // 128 floats
+  float* red = reinterpret_cast<float*>(smem + kMiscOff + 512);               // 32 floats
+  float* sgs = reinterpret_cast<float*>(smem + kMiscOff + 640);               // 16 floats
+  const uint32_t bar = smem_u32(smem + kMiscOff + 704);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + kMiscOff + 712);
 
   const uint32_t total = rows * blk_per_row;
   const uint32_t b0 = min(total, blockIdx.x * blocks_per_cta);
@@ -213,7 +216,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     const uint4 a = p[0], b = p[1];
     w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
   };
-  auto block_max = [&](const uint32_t (&w)[8]) {
+  auto block_max = [&](uint32_t i, const uint32_t (&w)[8]) {
     if (RHT) {
       float v[16];
       expand<true>(w, sm, v);
@@ -222,7 +225,9 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
       for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(v[j]));
       return a * 0.25f;
     }
-    return amax_packed8(w);
+    const float a = amax_packed8(w);
+    if (i - b0 < (uint32_t)kTabBlocks) amax_tab[i - b0] = (uint16_t)(__float_as_uint(a) >> 16);
+    return a;
   };
   // the streamed head, kBatch blocks per thread in flight before any of them is consumed
   for (uint32_t i = b0 + tid; i < s0; i += kBatch * kThreads) {
@@ -233,7 +238,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
       load_global(iu, w[u]);
     }
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) m = fmaxf(m, block_max(w[u]));
+    for (int u = 0; u < kBatch; ++u) m = fmaxf(m, block_max(min(i + u * kThreads, s0 - 1), w[u]));
   }
   if (stamper) ws->stamp[1] = global_ns();
   if (stash_blocks > 0) {
@@ -248,7 +253,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     for (uint32_t i = s0 + tid; i < b1; i += kThreads) {
       uint32_t w[8];
       load_stash(i, w);
-      m = fmaxf(m, block_max(w));
+      m = fmaxf(m, block_max(i, w));
     }
   }
   m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
@@ -311,7 +316,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
       amax_b *= 0.25f;                                   // H = butterfly / 4, an exact scaling
     } else {
       expand<false>(w, sm, v);
-      amax_b = amax_packed8(w);
+      amax_b = (i - b0 < (uint32_t)kTabBlocks) ? __uint_as_float((uint32_t)amax_tab[i - b0] << 16) : amax_packed8(w);
     }
     const uint32_t sf = block_scale_byte(amax_b, sc);
     const float recip = RHT ? recip_tab[sf] * 0.25f : recip_tab[sf];

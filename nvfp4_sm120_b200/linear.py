@@ -93,6 +93,27 @@ def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, tran
     return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose, amax=amax)
 
 
+class WeightQuantCache:
+    """quant(w) and quant(w.t()) of one weight, recomputed when the global step moves
+    (nvfp4_train.py:72-78).  One amax pass serves both layouts."""
+
+    def __init__(self):
+        self.step, self.wq_K, self.wq_N = -1, None, None
+
+    def get(self, weight, amax_reduce=None):
+        if not _AMORTIZE:
+            return None, None
+        if self.step != _STEP[0]:
+            w = weight.detach()
+            amax = tensor_amax(w)
+            if amax_reduce is not None:
+                amax_reduce(amax)
+            self.wq_K = quant_nvfp4(w, amax=amax)                      # [N, K], contraction K (fprop)
+            self.wq_N = quant_nvfp4(w, amax=amax, transpose=True)      # [K, N], contraction N (dgrad)
+            self.step = _STEP[0]
+        return self.wq_K, self.wq_N
+
+
 class FP4Linear(nn.Module):
     """Drop-in for nn.Linear(cin, cout, bias=False) with fp32 master weights (nvfp4_train.py:58-80)."""
 
@@ -104,27 +125,23 @@ class FP4Linear(nn.Module):
         self.register_buffer("H", hadamard16(device))
         g = torch.Generator().manual_seed(1)
         self.register_buffer("signs", (torch.randint(0, 2, (BLK,), generator=g).float() * 2 - 1).to(device))
-        self._cache_step = -1
-        self._wq_K = self._wq_N = None
+        self._cache = WeightQuantCache()
 
-    def _weight_quants(self, amax_reduce=None):
-        if not _AMORTIZE:
-            return None, None
-        step = _STEP[0]
-        if self._cache_step != step:
-            w = self.weight.detach()
-            if amax_reduce is None:
-                amax = tensor_amax(w)                      # one amax serves both layouts
-            else:
-                amax = tensor_amax(w)
-                amax_reduce(amax)
-            self._wq_K = quant_nvfp4(w, amax=amax)                      # [N, K], contraction K (fprop)
-            self._wq_N = quant_nvfp4(w, amax=amax, transpose=True)      # [K, N], contraction N (dgrad)
-            self._cache_step = step
-        return self._wq_K, self._wq_N
+    # the reference's field names (nvfp4_train.py:67-68)
+    @property
+    def _cache_step(self):
+        return self._cache.step
+
+    @property
+    def _wq_K(self):
+        return self._cache.wq_K
+
+    @property
+    def _wq_N(self):
+        return self._cache.wq_N
 
     def forward(self, x):
-        wq_K, wq_N = self._weight_quants()
+        wq_K, wq_N = self._cache.get(self.weight)
         return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N)
 
     def extra_repr(self):

@@ -1,0 +1,192 @@
+"""Multi-GPU forms of the FP4 path on one 8 x B200 box (one process per GPU, torch.distributed).
+
+The reference is single-GPU (it has no collective anywhere); these are the two shardings its
+path admits, each with exactly one exchange step:
+
+* tensor-parallel SwiGLU FFN: gate/up column-parallel (weight [h/p, d] per rank), down
+  row-parallel (weight [d, h/p]).  The per-tensor amax of every tensor that is split across
+  ranks (the weights, the hidden activation and its gradient) is max-reduced over the group
+  BEFORE quantizing, so every rank uses the global scale amax/2688 a single GPU would use and
+  the round-to-nearest bytes of a shard equal the corresponding slice of the 1-GPU result.  The
+  row-parallel output and the column-parallel input gradient are summed with an all-reduce.
+* data-parallel training: replicas, bucketed bf16 gradient all-reduce, per-rank Philox seed offset
+  so that the stochastic-rounding dither of different ranks is independent.
+
+The local linear is injected (`linear_fn`), which lets the collective logic run on CPU ranks
+(gloo) with a plain matmul; on GPUs it is FP4LinearFn."""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+# ------------------------------------------------------------------------------------------
+# collectives as autograd functions
+# ------------------------------------------------------------------------------------------
+class _CopyToGroup(torch.autograd.Function):
+    """Identity forward, all-reduce(SUM) backward: the input of a column-parallel linear."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous()
+        dist.all_reduce(g, op=dist.ReduceOp.SUM, group=ctx.group)
+        return g, None
+
+
+class _ReduceFromGroup(torch.autograd.Function):
+    """All-reduce(SUM) forward, identity backward: the output of a row-parallel linear."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        x = x.contiguous()
+        dist.all_reduce(x, op=dist.ReduceOp.SUM, group=group)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def amax_max_reducer(group=None):
+    """Callable that max-reduces a 1-element fp32 amax tensor over `group`, in place."""
+    def reduce_(amax):
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+        return amax
+    return reduce_
+
+
+def shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Rows [rank*n/world, (rank+1)*n/world) of w (the column-parallel shard of a [out, in] weight)."""
+    n = w.shape[0]
+    assert n % world == 0
+    return w[rank * (n // world):(rank + 1) * (n // world)].contiguous()
+
+
+def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Columns slice of w (the row-parallel shard of a [out, in] weight)."""
+    n = w.shape[1]
+    assert n % world == 0
+    return w[:, rank * (n // world):(rank + 1) * (n // world)].contiguous()
+
+
+def _fp4_linear_fn(x, w, H, signs, wq_K, wq_N, amax_reduce, sharded):
+    from .linear import FP4LinearFn
+    return FP4LinearFn.apply(x, w, H, signs, wq_K, wq_N, amax_reduce, sharded)
+
+
+# ------------------------------------------------------------------------------------------
+# tensor-parallel layers
+# ------------------------------------------------------------------------------------------
+class _ParallelLinearBase(nn.Module):
+    def __init__(self, weight_shard, group, linear_fn, device):
+        super().__init__()
+        self.group = group
+        self.weight = nn.Parameter(weight_shard.to(device))
+        self.linear_fn = linear_fn or _fp4_linear_fn
+        self.amax_reduce = amax_max_reducer(group)
+        if linear_fn is None:
+            from .linear import WeightQuantCache
+            from .quant import hadamard16
+            self._cache = WeightQuantCache()
+            self.register_buffer("H", hadamard16(device))
+            g = torch.Generator().manual_seed(1)
+            self.register_buffer("signs", (torch.randint(0, 2, (16,), generator=g).float() * 2 - 1).to(device))
+        else:
+            self._cache = None
+            self.H = self.signs = None
+
+    def _call(self, x, sharded):
+        wq_K = wq_N = None
+        if self._cache is not None:
+            wq_K, wq_N = self._cache.get(self.weight, self.amax_reduce)
+        return self.linear_fn(x, self.weight, self.H, self.signs, wq_K, wq_N, self.amax_reduce, sharded)
+
+
+class ColumnParallelFP4Linear(_ParallelLinearBase):
+    """y_local[*, out/p] = x @ W_local^T.  x is replicated; the output and its gradient are split
+    along the feature dim, so their amax is reduced; dX is summed over the group."""
+
+    def forward(self, x):
+        x = _CopyToGroup.apply(x, self.group)
+        return self._call(x, (False, True))
+
+
+class RowParallelFP4Linear(_ParallelLinearBase):
+    """y[*, out] = sum over ranks of x_local @ W_local^T.  The input is split along the feature dim
+    (its amax is reduced); the output is summed over the group and is then replicated."""
+
+    def forward(self, x_local):
+        y = self._call(x_local, (True, False))
+        return _ReduceFromGroup.apply(y, self.group)
+
+
+class TensorParallelSwiGLU(nn.Module):
+    """SwiGLU FFN y = down(silu(gate(x)) * up(x)) with d_model d and hidden h, sharded over `group`
+    (BASELINE config 4: d 4096, h 14336).  full_* are the unsharded [h, d], [h, d], [d, h] weights
+    every rank builds from the same seed; each rank keeps only its slice."""
+
+    def __init__(self, full_gate, full_up, full_down, group=None, linear_fn=None, device="cuda"):
+        super().__init__()
+        rank = dist.get_rank(group) if dist.is_initialized() else 0
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.gate = ColumnParallelFP4Linear(shard_rows(full_gate, rank, world), group, linear_fn, device)
+        self.up = ColumnParallelFP4Linear(shard_rows(full_up, rank, world), group, linear_fn, device)
+        self.down = RowParallelFP4Linear(shard_cols(full_down, rank, world), group, linear_fn, device)
+
+    def forward(self, x):
+        return self.down(F.silu(self.gate(x)) * self.up(x))
+
+
+# ------------------------------------------------------------------------------------------
+# data parallel
+# ------------------------------------------------------------------------------------------
+def broadcast_parameters(module: nn.Module, src: int = 0, group=None):
+    """Make every replica start from rank src's parameters and buffers."""
+    with torch.no_grad():
+        for t in list(module.parameters()) + list(module.buffers()):
+            dist.broadcast(t, src=src, group=group)
+
+
+def all_reduce_gradients(params, group=None, bucket_bytes: int = 64 << 20, wire_dtype=torch.bfloat16):
+    """Average the gradients of `params` over the group: gradients are packed into buckets of about
+    bucket_bytes in `wire_dtype` (bf16 on the wire, as the data-parallel config asks), summed with
+    one all-reduce per bucket, divided by the group size and copied back in their own dtype."""
+    world = dist.get_world_size(group)
+    grads = [p.grad for p in params if p.grad is not None]
+    esize = torch.empty((), dtype=wire_dtype).element_size()
+    bucket, size = [], 0
+
+    def flush():
+        nonlocal bucket, size
+        if not bucket:
+            return
+        flat = torch.cat([g.reshape(-1).to(wire_dtype) for g in bucket])
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+        flat = flat.float().div_(world)
+        off = 0
+        for g in bucket:
+            n = g.numel()
+            g.copy_(flat[off:off + n].view_as(g))
+            off += n
+        bucket, size = [], 0
+
+    for g in grads:
+        bucket.append(g)
+        size += g.numel() * esize
+        if size >= bucket_bytes:
+            flush()
+    flush()
+
+
+def seed_stochastic_rounding(base_seed: int, rank: int):
+    """Give each data-parallel rank its own Philox seed range (seeds advance by one per stochastic
+    quantization, nvfp4_cuda.py:160-162; ranks are 2^40 apart)."""
+    from . import quant
+    quant._SEED[0] = int(base_seed) + (int(rank) << 40)
