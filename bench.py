@@ -247,29 +247,41 @@ def run_gpu_arm(args, rank, world, local_rank):
     qd = torch.empty(ROWS, COLS // 2, dtype=torch.uint8, device=dev)
     sc = torch.empty(sm, sk, dtype=torch.uint8, device=dev)
     pts = torch.empty((), dtype=torch.float32, device=dev)
-    ws = quant_mod._workspace(dev)
-    sp = torch.cuda.current_stream().cuda_stream
-    iters = max(10, args.steps)
     kern = {}
+
+    def graph_time(launch, reps=20):
+        """Average device time of one launch: a CUDA graph of N_BUF launches (one per input tensor),
+        replayed; launches issued one by one from Python would measure the host instead."""
+        side2 = torch.cuda.Stream()
+        with torch.cuda.stream(side2):
+            for b in range(N_BUF):
+                launch(xs[b], side2.cuda_stream)
+            side2.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side2):
+                for b in range(N_BUF):
+                    launch(xs[b], torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            g.replay()
+        return time_events(lambda i: g.replay(), reps, torch.cuda.current_stream()) / N_BUF
+
     for mode in MODES:
         rht, sr = int(mode == "rht_sr"), int(mode != "rne")
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(iters)]
-        for i in range(iters):
-            x = xs[i % N_BUF]
-            ev[i][0].record()
+
+        def fused(x, sp_):
             lib.nvfp4_quantize_fused_bf16(x.data_ptr(), ROWS, COLS, COLS, sr, rht, signs.data_ptr(), SR_SEED, 0,
-                                          qd.data_ptr(), sc.data_ptr(), pts.data_ptr(), ws.data_ptr(), 64, sp)
-            ev[i][1].record()
-            x2 = xs[(i + 3) % N_BUF]
-            lib.nvfp4_amax_bf16(x2.data_ptr(), ROWS, COLS, COLS, rht, 0, signs.data_ptr(), amax_buf.data_ptr(), 1, sp)
-            ev[i][2].record()
-            lib.nvfp4_quantize_bf16(x2.data_ptr(), ROWS, COLS, COLS, 0, sr, rht, signs.data_ptr(), amax_buf.data_ptr(),
-                                    SR_SEED, 0, qd.data_ptr(), sc.data_ptr(), pts.data_ptr(), sp)
-            ev[i][3].record()
-        torch.cuda.synchronize()
-        t_fused = statistics.mean(e[0].elapsed_time(e[1]) for e in ev[2:])
-        t_amax = statistics.mean(e[1].elapsed_time(e[2]) for e in ev[2:])
-        t_quant = statistics.mean(e[2].elapsed_time(e[3]) for e in ev[2:])
+                                          qd.data_ptr(), sc.data_ptr(), pts.data_ptr(), ws2.data_ptr(), 64, sp_)
+
+        def amax_only(x, sp_):
+            lib.nvfp4_amax_bf16(x.data_ptr(), ROWS, COLS, COLS, rht, 0, signs.data_ptr(), amax_buf.data_ptr(), 1, sp_)
+
+        def quant_only(x, sp_):
+            lib.nvfp4_quantize_bf16(x.data_ptr(), ROWS, COLS, COLS, 0, sr, rht, signs.data_ptr(), amax_buf.data_ptr(),
+                                    SR_SEED, 0, qd.data_ptr(), sc.data_ptr(), pts.data_ptr(), sp_)
+
+        ws2 = torch.zeros(16, dtype=torch.int32, device=dev)
+        t_fused, t_amax, t_quant = graph_time(fused), graph_time(amax_only), graph_time(quant_only)
         kern[mode] = {"fused_us": t_fused * 1e3, "gbs": BYTES_PER_MODE / (t_fused * 1e-3) / 1e9,
                       "two_launch": {"amax_us": t_amax * 1e3, "quant_us": t_quant * 1e3,
                                      "gbs": BYTES_PER_MODE / ((t_amax + t_quant) * 1e-3) / 1e9}}

@@ -37,7 +37,8 @@ struct Workspace {          // 64 bytes of caller scratch: all zero before the f
   int error;                // sticky: 1 = the grid barrier gave up, 2 = a bulk copy never landed
   unsigned int done;
   unsigned long long stamp[5];   // diagnostics: globaltimer of CTA 0 at start, after the streamed
-  int pad[2];                    // amax, after the stashed amax, after the barrier, at the end
+                                 // amax, after the stashed amax, after the barrier, at the end
+  unsigned long long last_end;   // latest end over all CTAs of the last launch (diagnostics)
 };
 
 struct FastDiv {            // n / d for 0 <= n < 2^31 and a fixed d, as one mulhi and a shift
@@ -195,7 +196,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   }
   if (RHT && tid < 16) sgs[tid] = __ldg(signs16 + tid);
   const bool stamper = blockIdx.x == 0 && tid == 0;
-  if (stamper) ws->stamp[0] = global_ns();
+  if (stamper) { ws->stamp[0] = global_ns(); ws->last_end = 0ull; }
   __syncthreads();
   uint32_t sm[8];                 // sign-bit masks of the packed bf16 pairs (bit 15: even, bit 31: odd)
 #pragma unroll
@@ -360,6 +361,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   __syncthreads();
   if (stamper) ws->stamp[4] = global_ns();
   if (tid == 0) {
+    atomicMax(&ws->last_end, global_ns());
     __threadfence();
     if (atomicAdd(&ws->done, 1u) == gridDim.x - 1) {
       ws->amax = 0.0f;
