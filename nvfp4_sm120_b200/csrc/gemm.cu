@@ -14,16 +14,14 @@
 //               store bf16/fp32
 // All waits are bounded: a wait that gives up writes a code to *status, raises a CTA-wide abort
 // flag, and the kernel drains and frees its tensor memory before returning.
-#include <cuda.h>
-#include "common.cuh"
-#include "nvfp4_b200.h"
+// This one-CTA kernel serves M <= 128; larger problems go to the two-CTA kernel (gemm_2cta.cu).
+#include "gemm_common.cuh"
 
 namespace nvfp4 {
 namespace gemm {
 
 constexpr int kTileM = 128;
 constexpr int kTileN = 256;
-constexpr int kTileK = 256;                 // elements per K slice = 128 bytes per row
 constexpr int kStages = 4;
 constexpr int kABytes = kTileM * 128;       // 16 KiB
 constexpr int kBBytes = kTileN * 128;       // 32 KiB
@@ -32,124 +30,7 @@ constexpr int kSfbBytes = 2 * 4 * 512;      // 256 rows x 16 scales
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // 55296
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 512;
-constexpr int kGroupM = 16;                  // row tiles per rasterization group
 constexpr int kSfColsPerStage = 16 + 32;    // SFA 4 columns per K=64 block, SFB 8
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // a wait that lasts 2 s gives up
-
-enum : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3 };
-
-// ---- PTX wrappers -------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when it gave up (or another thread already raised the abort flag).
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 0u) {
-      if (*abort_flag != 0) return false;
-      if (global_ns() - t0 > kWaitLimitNs) return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 16 consecutive 32-bit columns of this warp's 32 TMEM lanes, from registers
-__device__ __forceinline__ void tc_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
-  asm volatile(
-      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, K-major operand rows of 128 bytes with the 128-byte swizzle:
-// 8-row groups are 1024 bytes apart (stride byte offset), descriptor version 1 (Blackwell).
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
-// Instruction descriptor of kind::mxf4nvf4: A/B format E2M1 (code 1), E4M3 scales (0), both K-major,
-// N >> 3 at bit 17, M >> 4 at bit 24, dense K = 64.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n) {
-  return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-struct Params {
-  const uint8_t* a_sf;
-  const uint8_t* b_sf;
-  const float* a_pts;
-  const float* b_pts;
-  void* d;
-  int64_t M, N, K, ldd;
-  int out_f32;
-  int32_t* status;
-};
-
-__device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status, int code) {
-  *abort_flag = 1;
-  if (status != nullptr) atomicCAS(status, 0, code);
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
@@ -311,43 +192,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         uint32_t r[32];
         tc_ld_32x32b_x32(taddr + c0, r);
         tc_wait_ld();
-        if (row < p.M) {
-          const int64_t col = n0 + c0;
-          const bool full = (col + 32 <= p.N);
-          if (p.out_f32) {
-            float* out = static_cast<float*>(p.d) + row * p.ldd + col;
-            if (full && ((p.ldd & 3) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(out + j) =
-                    make_float4(__uint_as_float(r[j]) * alpha, __uint_as_float(r[j + 1]) * alpha,
-                                __uint_as_float(r[j + 2]) * alpha, __uint_as_float(r[j + 3]) * alpha);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col + j < p.N) out[j] = __uint_as_float(r[j]) * alpha;
-            }
-          } else {
-            __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.d) + row * p.ldd + col;
-            if (full && ((p.ldd & 7) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * q]) * alpha,
-                                                           __uint_as_float(r[j + 2 * q + 1]) * alpha);
-                  w[q] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                *reinterpret_cast<uint4*>(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col + j < p.N) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * alpha);
-            }
-          }
-        }
+        if (row < p.M) store_row_chunk(p, row, n0 + c0, r, alpha);
       }
     }
   }
@@ -359,55 +204,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   }
 }
 
-// ---- host side ------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  }
-  return fn;
-}
-
-// packed E2M1 operand [rows, K/2] bytes, K-major -> 2-D byte tensor map, box 128 bytes x box_rows
-static bool make_operand_map(CUtensorMap* map, const uint8_t* ptr, int64_t rows, int64_t k, int box_rows) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)(k / 2), (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)(k / 2)};
-  cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1u, 1u};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(ptr), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 }  // namespace gemm
 }  // namespace nvfp4
 
-extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
-                          const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
-                          int64_t K, int64_t ldd, int32_t* status, void* stream_) {
-  using namespace nvfp4::gemm;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!a_q || !a_sf || !a_pts || !b_q || !b_sf || !b_pts || !d) return NVFP4_E_NULL;
-  if (M <= 0 || N <= 0 || K <= 0 || (K & 31) != 0 || ldd < N) return NVFP4_E_SHAPE;
-  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return NVFP4_E_SHAPE;
-  if (out_dtype != NVFP4_OUT_BF16 && out_dtype != NVFP4_OUT_F32) return NVFP4_E_MODE;
-  auto mis = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
-  if (mis(a_q, 16) || mis(b_q, 16) || mis(a_sf, 16) || mis(b_sf, 16) || mis(d, 16)) return NVFP4_E_ALIGN;
-  CUtensorMap map_a, map_b;
-  if (!make_operand_map(&map_a, a_q, M, K, kTileM) || !make_operand_map(&map_b, b_q, N, K, kTileN))
-    return NVFP4_E_DRIVER;
+namespace nvfp4 { namespace gemm {
+// launch of the one-CTA kernel (arguments already validated)
+int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
@@ -416,10 +218,9 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
       return NVFP4_E_LAUNCH;
     attr_set[dev] = true;
   }
-  Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status};
-  const int64_t n_tiles = ((N + kTileN - 1) / kTileN) * ((M + kTileM - 1) / kTileM);
+  const int64_t n_tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kTileM - 1) / kTileM);
   if (n_tiles > 0x7fffffffLL) return NVFP4_E_SHAPE;
-  dim3 grid((unsigned)n_tiles);
-  gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  gemm_kernel<<<dim3((unsigned)n_tiles), kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
+}}  // namespace nvfp4::gemm
