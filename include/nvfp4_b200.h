@@ -123,6 +123,13 @@ int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
                void* d, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t ldd,
                int32_t* status, void* stream);
 
+/*
+ * Kernel choice of nvfp4_gemm for this process: 0 = automatic (the default), 1 = always the
+ * one-CTA 128x256 kernel, 2 = always the two-CTA 256x256 kernel.  For tuning and tests; results
+ * are the same to rounding of the accumulation order.  No counterpart in the reference.
+ */
+int nvfp4_gemm_set_mode(int mode);
+
 #ifdef __cplusplus
 }
 #endif

@@ -14,7 +14,7 @@
 //               store bf16/fp32
 // All waits are bounded: a wait that gives up writes a code to *status, raises a CTA-wide abort
 // flag, and the kernel drains and frees its tensor memory before returning.
-// This one-CTA kernel serves M <= 128; larger problems go to the two-CTA kernel (gemm_2cta.cu).
+// gemm_2cta.cu holds the cta_group::2 variant (256 x 256 per CTA pair) and the C entry point.
 #include "gemm_common.cuh"
 
 namespace nvfp4 {

@@ -9,11 +9,11 @@
 //   TMA tensor copies: A rows [m0 + 128 r, +128), B rows [n0 + 128 r, +128)  -> 128B-swizzled smem,
 //     completing on the LEADER's (rank 0) "full" barrier (cta_group::2 form, no multicast);
 //   bulk copies: scale tiles of its own A rows and of all 256 B rows -> smem, on a local barrier;
-//   warps 2..5: scale factors smem -> registers -> tensor memory (tcgen05.st), then arrive on the
-//     leader's "scales ready" barrier (remote arrive for rank 1);
+//   warps 2..9 (two sets of four, alternating K slices): scale factors smem -> registers -> tensor
+//     memory (tcgen05.st), then arrive on the leader's "scales ready" barrier (remote for rank 1);
 //   leader's warp 1, one lane: waits for both, issues four MMAs (M 256 = 128 per CTA, N 256, K 64),
 //     then commits to the "empty" barrier of BOTH CTAs (two commits, one local, one remote).
-// Each CTA's warps 2..5 finally drain their own 128 accumulator rows.  All waits are bounded; the
+// Each CTA's warps 2..9 finally drain their own 128 accumulator rows.  All waits are bounded; the
 // kernel ends with a cluster barrier before the paired tensor-memory free.
 #include "gemm_common.cuh"
 
@@ -30,7 +30,7 @@ constexpr int kSfaBytes = 4 * 512;
 constexpr int kSfbBytes = 2 * 4 * 512;
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;      // 38912
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;             // producer, MMA issuer, and two sets of four scale/epilogue warps
 constexpr int kSfColsPerStage = 48;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -47,8 +47,10 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// Remote arrive, relaxed: the tensor-memory stores it announces are already complete
+// (tcgen05.wait::st precedes it), and a release at cluster scope costs ~1100 cycles here.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
                                                  uint32_t bar_cluster_addr) {
@@ -189,10 +191,11 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     }
   } else {
     // ------------------------------ scale factors, then epilogue ------------------------------
-    const int quad = warp & 3;
+    const int quad = warp & 3;                    // tensor-memory lanes 32 * quad .. + 31
+    const int set = (warp - 2) >> 2;              // the two sets of four warps take alternate K slices
     bool ok = true;
     const uint32_t leader_ready0 = map_to_cta(sready_bar(0), 0);
-    for (int kt = 0; kt < num_kt && ok; ++kt) {
+    for (int kt = set; kt < num_kt && ok; kt += 2) {
       const int s = kt % kStages;
       if (lane == 0) ok = mbar_wait(sfull_bar(s), (kt / kStages) & 1, abort_flag);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -219,7 +222,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(leader_ready0 + 8u * s);
+      if (lane == 0) { if (leader) mbar_arrive(sready_bar(s)); else mbar_arrive_cluster(leader_ready0 + 8u * s); }
     }
     if (ok && lane == 0) {
       ok = mbar_wait(acc_bar, 0, abort_flag);
@@ -232,7 +235,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       const int64_t row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
-      for (int c0 = 0; c0 < kTileN; c0 += 32) {
+      for (int c0 = 128 * set; c0 < 128 * set + 128; c0 += 32) {     // each set drains half of the columns
         if (n0 + c0 >= p.N) break;
         uint32_t r[32];
         tc_ld_32x32b_x32(taddr + c0, r);
@@ -272,7 +275,16 @@ namespace nvfp4 { namespace gemm {
 int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream);
 }}
 
-// M <= 128 has no second row tile to pair: the one-CTA kernel serves it; everything else runs on pairs.
+static int g_gemm_mode = 0;
+extern "C" int nvfp4_gemm_set_mode(int mode) {
+  if (mode < 0 || mode > 2) return NVFP4_E_MODE;
+  g_gemm_mode = mode;
+  return NVFP4_OK;
+}
+
+// Automatic choice: the one-CTA kernel.  Measured on B200 it is as fast or faster than the paired
+// kernel on every shape tried (both top out near 180-200 cycles per K=64 MMA step), and it wastes
+// nothing when M is not a multiple of 256; the paired kernel stays selectable (mode 2) and tested.
 extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
                           const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
                           int64_t K, int64_t ldd, int32_t* status, void* stream_) {
@@ -284,7 +296,7 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
   if (out_dtype != NVFP4_OUT_BF16 && out_dtype != NVFP4_OUT_F32) return NVFP4_E_MODE;
   auto mis = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
   if (mis(a_q, 16) || mis(b_q, 16) || mis(a_sf, 16) || mis(b_sf, 16) || mis(d, 16)) return NVFP4_E_ALIGN;
-  const bool pair = M > 128;
+  const bool pair = g_gemm_mode == 2;
   CUtensorMap map_a, map_b;
   if (!make_operand_map(&map_a, a_q, M, K, 128) || !make_operand_map(&map_b, b_q, N, K, pair ? 128 : 256))
     return NVFP4_E_DRIVER;

@@ -22,8 +22,11 @@ def main():
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 one-CTA kernel, 2 two-CTA kernel")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
+    from nvfp4_sm120_b200 import _lib
+    _lib.lib().nvfp4_gemm_set_mode(a.gemm_mode)
     g = torch.Generator(device=dev).manual_seed(0)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if a.case == "quant":

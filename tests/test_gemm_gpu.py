@@ -36,6 +36,26 @@ def test_gemm_fp32_out_matches_dequant_matmul(Q, mnk):
     assert torch.allclose(got, ref, rtol=2e-3, atol=2e-3 * ref.abs().max().item())
 
 
+@pytest.mark.parametrize("mnk", [(256, 512, 512), (130, 200, 320), (384, 768, 2048), (48, 80, 64), (1024, 1024, 4096)])
+def test_two_cta_kernel_matches(Q, mnk):
+    """The cta_group::2 kernel (mode 2) gives the one-CTA kernel's result and meets the tolerance."""
+    from nvfp4_sm120_b200 import _lib
+    m, n, k = mnk
+    qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 12).cuda())
+    qb = Q.quant_nvfp4(O.synthetic_tensor(n, k, 13).cuda())
+    try:
+        _lib.lib().nvfp4_gemm_set_mode(1)
+        one = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.float32).cpu()
+        _lib.lib().nvfp4_gemm_set_mode(2)
+        two = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.float32).cpu()
+    finally:
+        _lib.lib().nvfp4_gemm_set_mode(0)
+    assert Q.gemm_status() == 0
+    ref = _ref_from_gpu_quant(qa, qb, m, n, k)
+    assert ((two - ref).norm() / ref.norm()).item() < REL_TOL
+    assert torch.allclose(one, two, rtol=1e-5, atol=1e-5 * ref.abs().max().item())
+
+
 def test_gemm_bf16_out_is_rounded_fp32(Q):
     m, n, k = 256, 512, 1024
     qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 4).cuda())
