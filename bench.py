@@ -369,7 +369,9 @@ def run_gpu_arm(args, rank, world, local_rank):
 
 
 def extras(Q, dev, bf16_peak, peak_kind):
-    """FP4 GEMM throughput on BASELINE config 3 shapes with bf16 torch.matmul alongside."""
+    """Beside the headline: FP4 GEMM throughput on BASELINE config 3 shapes with bf16 torch.matmul
+    alongside, and the SwiGLU FFN of config 4 (d 4096, h 14336, 8 x 4096 tokens) forward+backward in
+    FP4 (amortized weight quantization) against the same block in bf16."""
     out = {"gemm": []}
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     for (m, n, k) in [(4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384), (16384, 4096, 14336)]:
@@ -378,8 +380,10 @@ def extras(Q, dev, bf16_peak, peak_kind):
         Bt = torch.randn(n, k, device=dev, dtype=torch.bfloat16, generator=g)
         qa, qb = Q.quant_nvfp4(A), Q.quant_nvfp4(Bt)
         d = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+
         def fp4(_):
             Q.nvfp4_mm(qa, qb.t(), out=d)
+
         def bf16(_):
             torch.matmul(A, Bt.t(), out=d)
         res = {}
@@ -398,6 +402,44 @@ def extras(Q, dev, bf16_peak, peak_kind):
                             "frac_of_9pf_datasheet": res["fp4"] / 9000.0})
         del A, Bt, qa, qb, d
     out["gemm_peak_kind"] = f"4 x {peak_kind} bf16 burst ({bf16_peak} TF/s)"
+    del flush
+    torch.cuda.empty_cache()
+
+    from nvfp4_sm120_b200.ffn import SwiGLUFFN, ffn_flops
+    d_model, hidden, tokens, micro = 4096, 14336, 4096, 8
+    g = torch.Generator(device=dev).manual_seed(4)
+    xs = [torch.randn(tokens, d_model, device=dev, dtype=torch.bfloat16, generator=g).requires_grad_(True)
+          for _ in range(micro)]
+    gy = torch.randn(tokens, d_model, device=dev, dtype=torch.bfloat16, generator=g)
+    ffn = {}
+    Q.set_amortize(True)
+    for name in ("fp4", "bf16"):
+        m = SwiGLUFFN(d_model, hidden, use_fp4=(name == "fp4"), device=dev, seed=4)
+        if name == "bf16":
+            m = m.to(torch.bfloat16)
+
+        def step():
+            Q.mark_step()
+            for x in xs:
+                y = m(x)
+                torch.autograd.grad(y, [x] + list(m.parameters()), grad_outputs=gy)
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
+            step()
+        e1.record()
+        e1.synchronize()
+        ms = e0.elapsed_time(e1) / 3
+        ffn[name] = {"ms_per_step": ms, "tflops": micro * ffn_flops(tokens, d_model, hidden) / ms / 1e9}
+        del m
+        torch.cuda.empty_cache()
+    Q.set_amortize(False)
+    ffn["speedup_vs_bf16"] = ffn["bf16"]["ms_per_step"] / ffn["fp4"]["ms_per_step"]
+    ffn["config"] = "SwiGLU d4096 h14336, 8 microbatches x 4096 tokens, fprop RNE / dgrad SR / wgrad RHT+SR, 1 GPU"
+    out["ffn_fwd_bwd"] = ffn
     out["gemm_status"] = Q.gemm_status()
     return out
 

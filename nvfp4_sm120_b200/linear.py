@@ -105,6 +105,8 @@ class WeightQuantCache:
             return None, None
         if self.step != _STEP[0]:
             w = weight.detach()
+            if w.dtype != torch.bfloat16:
+                w = w.to(torch.bfloat16)          # one cast of the fp32 master weight serves all three kernels
             amax = tensor_amax(w)
             if amax_reduce is not None:
                 amax_reduce(amax)

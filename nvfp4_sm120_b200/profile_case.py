@@ -13,7 +13,7 @@ import nvfp4_sm120_b200 as Q
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["quant", "gemm"])
+    ap.add_argument("case", choices=["quant", "gemm", "ffn"])
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--mode", default="rne", choices=["rne", "sr", "rht_sr"])
@@ -21,6 +21,11 @@ def main():
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--d", type=int, default=4096)
+    ap.add_argument("--h", type=int, default=14336)
+    ap.add_argument("--micro", type=int, default=8)
+    ap.add_argument("--bf16", action="store_true", help="ffn: bf16 nn.Linear comparator instead of FP4Linear")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 one-CTA kernel, 2 two-CTA kernel")
     a = ap.parse_args()
@@ -29,6 +34,34 @@ def main():
     _lib.lib().nvfp4_gemm_set_mode(a.gemm_mode)
     g = torch.Generator(device=dev).manual_seed(0)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if a.case == "ffn":
+        from nvfp4_sm120_b200.ffn import SwiGLUFFN, ffn_flops
+        Q.set_amortize(True)
+        m = SwiGLUFFN(a.d, a.h, use_fp4=not a.bf16, device=dev, seed=4)
+        if a.bf16:
+            m = m.to(torch.bfloat16)
+        xs = [torch.randn(a.tokens, a.d, device=dev, dtype=torch.bfloat16, generator=g).requires_grad_(True)
+              for _ in range(a.micro)]
+        gys = [torch.randn(a.tokens, a.d, device=dev, dtype=torch.bfloat16, generator=g) for _ in range(2)]
+
+        def step():
+            Q.mark_step()
+            for i, x in enumerate(xs):
+                y = m(x)
+                torch.autograd.grad(y, [x] + list(m.parameters()), grad_outputs=gys[i % 2])
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.iters):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / a.iters
+        fl = a.micro * ffn_flops(a.tokens, a.d, a.h)
+        print(f"ffn {'bf16' if a.bf16 else 'fp4'} d={a.d} h={a.h} tokens={a.tokens} x {a.micro}: {ms:.2f} ms/step, "
+              f"{fl / ms / 1e9:.0f} TFLOP/s")
+        return
     if a.case == "quant":
         x = torch.randn(a.rows, a.cols, device=dev, dtype=torch.bfloat16, generator=g)
         signs = torch.ones(16, device=dev)
