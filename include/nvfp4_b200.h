@@ -108,6 +108,24 @@ int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t cols, int64_t
                               void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * nvfp4_quantize_fused_bf16 for callers that cannot allocate device memory where they call from
+ * (a C / FFI binding inside a runtime that gave all of HBM to its own pool, a callback that must
+ * not hit cudaMalloc's implicit synchronisation): the kernel's scratch is a 256-byte device array
+ * inside the library instead of a caller workspace, so the caller passes inputs and outputs only.
+ * The call allocates nothing.  Same outputs, bit for bit.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the array: calls that can overlap on the GPU (different
+ *     streams) race on it.  Calls on one stream are safe; each call clears what it needs.
+ *   - Limit: rows * cols / 16 <= 2^31 - 1, otherwise NVFP4_E_LIMIT.
+ * This entry point has no counterpart in the reference.
+ */
+int nvfp4_quantize_static_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                               int mode, int rht, const float* signs16,
+                               uint64_t philox_seed, uint64_t philox_offset,
+                               uint8_t* qdata, uint8_t* scales, float* pts_out, void* stream);
+
+/*
  * Block-scaled FP4 GEMM  D[M, N] = (A . sfA) (B . sfB)^T * (*a_pts) * (*b_pts)
  * with fp32 accumulation on the tcgen05 tensor cores.
  *   a_q [M, K/2], b_q [N, K/2]: packed E2M1, both K-major; a_sf, b_sf: swizzled E4M3 scales;

@@ -450,3 +450,50 @@ extern "C" int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t co
   cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, kSmemBytes, stream);
   return e == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Variant for callers that cannot allocate device memory
+// ---------------------------------------------------------------------------------------------
+// Some users of this library reach it from places where a device allocation is not an option: a C
+// or FFI binding running inside a host runtime that handed all of HBM to its own pool at start-up,
+// or a callback in which the implicit synchronisation of cudaMalloc is not acceptable.  For them
+// the 64-byte scratch of the single-launch quantizer lives in this file-scope device array instead
+// of a caller-provided workspace.  Every GPU that loads the library holds these 256 bytes until the
+// process exits.  All calls on a device share the array: calls that overlap on the GPU (different
+// streams) race on it; calls on one stream do not.
+static __device__ __align__(256) unsigned char g_static_scratch[256];
+
+// Largest tensor the no-allocation entry point accepts: 2^31 - 1 blocks of 16 elements (the same
+// bound the single-launch kernel has); the scratch itself does not grow with the tensor.
+static constexpr long long kStaticMaxBlocks = (1ll << 31) - 1;
+
+#include <mutex>
+static std::mutex g_static_mutex;
+static void* g_static_ptr[64] = {};
+
+extern "C" int nvfp4_quantize_static_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
+                                          const float* signs16, uint64_t seed, uint64_t offset, uint8_t* qdata,
+                                          uint8_t* scales, float* pts_out, void* stream_) {
+  if (rows <= 0 || cols <= 0 || (cols & 15) != 0) return NVFP4_E_SHAPE;
+  if (rows > kStaticMaxBlocks || (cols / 16) > kStaticMaxBlocks / rows) return NVFP4_E_LIMIT;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
+  void* ptr = nullptr;
+  {
+    // Set-up, once per device, with that device current: the array's name is only a host-side
+    // handle here, so the device address has to be asked for before it can be given to a kernel.
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return NVFP4_E_LAUNCH;
+      g_static_ptr[dev] = p;
+    }
+    ptr = g_static_ptr[dev];
+  }
+  // The array keeps whatever the previous call (or an aborted one) left: the words the kernel
+  // expects to find zero are cleared on the stream first.  This is a memset, not an allocation.
+  if (cudaMemsetAsync(ptr, 0, sizeof(Workspace), static_cast<cudaStream_t>(stream_)) != cudaSuccess)
+    return NVFP4_E_LAUNCH;
+  return nvfp4_quantize_fused_bf16(x, rows, cols, ld, mode, rht, signs16, seed, offset, qdata, scales, pts_out, ptr,
+                                   sizeof(Workspace), stream_);
+}
