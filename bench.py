@@ -337,7 +337,9 @@ def run_gpu_arm(args, rank, world, local_rank):
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_ms, "note": "pinned host input -> device, three quantizations, results -> pinned host"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                     "frac": achieved / hbm_peak, "traffic": 69.7e6, "peak_kind": peak_kind,
+                     "traffic_note": "dram read+write bytes per launch, ncu capture of the same kernel and size "
+                                     "(profiles/quant_fused_8192x4096.md)",
                      "kernel": "quant_fused_kernel, one launch per mode (algorithmic bytes of the three modes / summed event time)"},
         "modes": kern,
         "quantizer_error_word": quant_mod.fused_error(dev),
