@@ -143,6 +143,8 @@ class FP4Linear(nn.Module):
         return self._cache.wq_N
 
     def forward(self, x):
+        if x.is_cuda and torch.is_autocast_enabled("cuda"):
+            x = x.to(torch.get_autocast_dtype("cuda"))       # what autocast does for nn.Linear
         wq_K, wq_N = self._cache.get(self.weight)
         return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N)
 

@@ -1,0 +1,124 @@
+"""Decoder-only language models whose linears are FP4Linear: the callers of the hot path.
+
+`GPT` is the nanoGPT-style model of the reference's scaling study (scaling/train_text.py:37-92:
+RMSNorm, rotary positions, grouped-query attention, squared-ReLU MLP, tied head, first block and the
+last `hp_tail` blocks kept in high precision); `LM` is the small model of its addition-task trainer
+(nvfp4_train.py:101-140: same block, untied head, hp rule `i == 0 or i >= n_layers - hp_tail`).
+Attention, norms, embedding and head stay bf16/fp32 torch ops, as in the reference."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .linear import make_linear
+
+
+@dataclass
+class GPTConfig:
+    vocab: int = 50257
+    dim: int = 768
+    n_layers: int = 12
+    n_heads: int = 12
+    n_kv_heads: int = 12
+    mlp_ratio: int = 4
+    use_fp4: bool = True
+    hp_tail: int = 1           # last blocks kept dense; block 0 always is (scaling/train_text.py:66-67)
+    tie_head: bool = True
+
+
+def rotary_tables(seq_len, head_dim, device):
+    """cos / sin tables [1, 1, T, head_dim / 2] with base 10000 (nvfp4_train.py:91-98)."""
+    half = head_dim // 2
+    freq = 10000.0 ** (-torch.arange(half, device=device, dtype=torch.float32) / half)
+    angle = torch.arange(seq_len, device=device, dtype=torch.float32)[:, None] * freq[None, :]
+    return angle.cos()[None, None], angle.sin()[None, None]
+
+
+def apply_rotary(x, cos, sin):
+    """Rotate the two halves of the head dimension against each other."""
+    a, b = x.chunk(2, dim=-1)
+    return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+
+
+class DecoderBlock(nn.Module):
+    def __init__(self, dim, n_heads, n_kv_heads, hidden, use_fp4, device):
+        super().__init__()
+        assert dim % n_heads == 0 and n_heads % n_kv_heads == 0
+        self.n_heads, self.n_kv, self.head_dim = n_heads, n_kv_heads, dim // n_heads
+        self.norm_attn, self.norm_mlp = nn.RMSNorm(dim, device=device), nn.RMSNorm(dim, device=device)
+        kv_dim = n_kv_heads * self.head_dim
+        self.q = make_linear(dim, dim, use_fp4, device)
+        self.k = make_linear(dim, kv_dim, use_fp4, device)
+        self.v = make_linear(dim, kv_dim, use_fp4, device)
+        self.o = make_linear(dim, dim, use_fp4, device)
+        self.up = make_linear(dim, hidden, use_fp4, device)
+        self.down = make_linear(hidden, dim, use_fp4, device)
+
+    def forward(self, x, cos, sin):
+        B, T, _ = x.shape
+        h = self.norm_attn(x)
+        split = lambda t, n: t.view(B, T, n, self.head_dim).transpose(1, 2)
+        q, k, v = split(self.q(h), self.n_heads), split(self.k(h), self.n_kv), split(self.v(h), self.n_kv)
+        q, k = apply_rotary(q, cos, sin), apply_rotary(k, cos, sin)
+        if self.n_kv != self.n_heads:
+            rep = self.n_heads // self.n_kv
+            k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
+        att = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        x = x + self.o(att.transpose(1, 2).reshape(B, T, -1))
+        return x + self.down(F.relu(self.up(self.norm_mlp(x))).square())
+
+
+class GPT(nn.Module):
+    def __init__(self, cfg: GPTConfig, device="cuda"):
+        super().__init__()
+        self.cfg = cfg
+        self.emb = nn.Embedding(cfg.vocab, cfg.dim, device=device)
+        fp4_at = lambda i: cfg.use_fp4 and not (i == 0 or i >= cfg.n_layers - cfg.hp_tail)
+        self.blocks = nn.ModuleList(
+            DecoderBlock(cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.mlp_ratio * cfg.dim, fp4_at(i), device)
+            for i in range(cfg.n_layers))
+        self.norm = nn.RMSNorm(cfg.dim, device=device)
+        self.head = nn.Linear(cfg.dim, cfg.vocab, bias=False, device=device)
+        if cfg.tie_head:
+            self.head.weight = self.emb.weight
+        for m in self.modules():
+            if isinstance(m, (nn.Linear, nn.Embedding)):
+                nn.init.normal_(m.weight, std=0.02)
+        self._rope = None
+
+    def forward(self, idx, targets=None):
+        T = idx.shape[1]
+        if self._rope is None or self._rope[0].shape[2] != T or self._rope[0].device != idx.device:
+            self._rope = rotary_tables(T, self.cfg.dim // self.cfg.n_heads, idx.device)
+        cos, sin = self._rope
+        x = self.emb(idx)
+        for blk in self.blocks:
+            x = blk(x, cos, sin)
+        logits = self.head(self.norm(x))
+        if targets is None:
+            return logits, None
+        return logits, F.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), targets.reshape(-1))
+
+    def num_params(self):
+        """Non-embedding parameter count (the tied head counts once, as the embedding)."""
+        return sum(p.numel() for p in self.parameters()) - self.emb.weight.numel()
+
+    def fp4_linears(self):
+        from .linear import FP4Linear
+        return [m for m in self.modules() if isinstance(m, FP4Linear)]
+
+
+class LM(GPT):
+    """The addition-task model of nvfp4_train.py:126-140: untied head, hp_tail counted from the end,
+    block 0 dense when FP4 is on."""
+
+    def __init__(self, vocab, dim, nl, nh, nkv, hd, ffn, use_fp4, hp_tail=0, device="cuda"):
+        assert hd * nh == dim and ffn % dim == 0
+        super().__init__(GPTConfig(vocab=vocab, dim=dim, n_layers=nl, n_heads=nh, n_kv_heads=nkv,
+                                   mlp_ratio=ffn // dim, use_fp4=use_fp4, hp_tail=hp_tail, tie_head=False), device)
+
+    def forward(self, idx):
+        return super().forward(idx)[0]
