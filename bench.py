@@ -363,11 +363,58 @@ def run_gpu_arm(args, rank, world, local_rank):
                                 "sample": f"{rows} of {ROWS} rows x {COLS} cols, three modes, best of 2"}
         if not args.no_extras:
             line["extras"] = extras(Q, dev, bf16_peak, peak_kind)
+    if world > 1 and not args.no_extras:
+        tp = extras_tensor_parallel(Q, dev, rank, world, dist)
+        if rank == 0:
+            line["extras"] = {"ffn_tensor_parallel": tp}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def extras_tensor_parallel(Q, dev, rank, world, dist):
+    """BASELINE config 4 over `world` GPUs: SwiGLU d 4096 / h 14336 split column- (gate, up) and row-wise
+    (down), 8 microbatches x 4096 tokens, forward + backward, amortized weight quantization; NCCL
+    all-reduce of the amax words and of the row-parallel output / column-parallel input gradient.
+    Strong scaling: the same total work on more GPUs.  Timed on the device, max over ranks."""
+    from nvfp4_sm120_b200 import parallel as P
+    from nvfp4_sm120_b200.ffn import ffn_flops
+    d_model, hidden, tokens, micro = 4096, 14336, 4096, 8
+    g = torch.Generator(device=dev).manual_seed(4 + rank)
+    bd, bh = 1.0 / d_model ** 0.5, 1.0 / hidden ** 0.5
+    hs = hidden // world
+    mk = lambda r, c, b: (torch.rand(r, c, device=dev, generator=g) * 2 - 1) * b
+    ffn = P.TensorParallelSwiGLU(mk(hs, d_model, bd), mk(hs, d_model, bd), mk(d_model, hs, bh), device=dev)
+    gx = torch.Generator(device=dev).manual_seed(40)              # activations are replicated
+    xs = [torch.randn(tokens, d_model, device=dev, dtype=torch.bfloat16, generator=gx).requires_grad_(True)
+          for _ in range(micro)]
+    gy = torch.randn(tokens, d_model, device=dev, dtype=torch.bfloat16, generator=gx)
+    Q.set_amortize(True)
+
+    def step():
+        Q.mark_step()
+        for x in xs:
+            y = ffn(x)
+            torch.autograd.grad(y, [x] + list(ffn.parameters()), grad_outputs=gy)
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(3):
+        step()
+    e1.record()
+    e1.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / 3], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    Q.set_amortize(False)
+    ms = float(t.item())
+    return {"ms_per_step": ms, "tflops_all_gpus": micro * ffn_flops(tokens, d_model, hidden) / ms / 1e9,
+            "scaling": "strong", "tp": world, "gemm_status": Q.gemm_status(),
+            "config": "SwiGLU d4096 h14336, 8 microbatches x 4096 tokens, fwd+bwd, TP over NCCL"}
 
 
 def extras(Q, dev, bf16_peak, peak_kind):

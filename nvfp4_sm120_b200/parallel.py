@@ -129,16 +129,21 @@ class RowParallelFP4Linear(_ParallelLinearBase):
 
 class TensorParallelSwiGLU(nn.Module):
     """SwiGLU FFN y = down(silu(gate(x)) * up(x)) with d_model d and hidden h, sharded over `group`
-    (BASELINE config 4: d 4096, h 14336).  full_* are the unsharded [h, d], [h, d], [d, h] weights
-    every rank builds from the same seed; each rank keeps only its slice."""
+    (BASELINE config 4: d 4096, h 14336).  Built from this rank's shards: gate/up [h/p, d], down [d, h/p];
+    `from_full` slices them out of the unsharded [h, d], [h, d], [d, h] weights."""
 
-    def __init__(self, full_gate, full_up, full_down, group=None, linear_fn=None, device="cuda"):
+    def __init__(self, gate_shard, up_shard, down_shard, group=None, linear_fn=None, device="cuda"):
         super().__init__()
+        self.gate = ColumnParallelFP4Linear(gate_shard, group, linear_fn, device)
+        self.up = ColumnParallelFP4Linear(up_shard, group, linear_fn, device)
+        self.down = RowParallelFP4Linear(down_shard, group, linear_fn, device)
+
+    @classmethod
+    def from_full(cls, full_gate, full_up, full_down, group=None, linear_fn=None, device="cuda"):
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.gate = ColumnParallelFP4Linear(shard_rows(full_gate, rank, world), group, linear_fn, device)
-        self.up = ColumnParallelFP4Linear(shard_rows(full_up, rank, world), group, linear_fn, device)
-        self.down = RowParallelFP4Linear(shard_cols(full_down, rank, world), group, linear_fn, device)
+        return cls(shard_rows(full_gate, rank, world), shard_rows(full_up, rank, world),
+                   shard_cols(full_down, rank, world), group, linear_fn, device)
 
     def forward(self, x):
         return self.down(F.silu(self.gate(x)) * self.up(x))

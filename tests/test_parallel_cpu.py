@@ -54,7 +54,7 @@ def _worker(rank, world, port, results):
     d, h, T = 32, 64, 16
     gate, up, down = torch.randn(h, d), torch.randn(h, d), torch.randn(d, h)
     x = torch.randn(T, d, requires_grad=True)
-    ffn = P.TensorParallelSwiGLU(gate, up, down, linear_fn=_linear_fn, device="cpu")
+    ffn = P.TensorParallelSwiGLU.from_full(gate, up, down, linear_fn=_linear_fn, device="cpu")
     y = ffn(x)
     y.square().sum().backward()
     # unsharded reference with the same fake scaling and no group

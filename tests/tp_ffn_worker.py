@@ -45,7 +45,7 @@ def main():
         yr = ref(xr)
         yr.backward(gy.to(dev))
         # tensor parallel
-        tp = P.TensorParallelSwiGLU(gate, up, down, device=dev)
+        tp = P.TensorParallelSwiGLU.from_full(gate, up, down, device=dev)
         xt = x.to(dev).requires_grad_(True)
         quant._SEED[0] = 100
         yt = tp(xt)
