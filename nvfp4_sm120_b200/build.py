@@ -12,6 +12,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 LIB = os.path.join(PKG, "libnvfp4_b200.so")
+CLI = os.path.join(PKG, "nvfp4_gemm_cli")          # stand-alone C driver of the ABI (csrc/tools)
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--threads", "4"]
 
@@ -22,11 +23,11 @@ def sources():
 
 def _deps():
     return sources() + glob.glob(os.path.join(PKG, "csrc", "*.cuh")) + \
-        glob.glob(os.path.join(ROOT, "include", "*.h"))
+        glob.glob(os.path.join(ROOT, "include", "*.h")) + glob.glob(os.path.join(PKG, "csrc", "tools", "*.cu"))
 
 
 def up_to_date():
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(CLI):
         return False
     t = os.path.getmtime(LIB)
     return all(os.path.getmtime(p) <= t for p in _deps())
@@ -47,6 +48,13 @@ def build(force=False, verbose=False):
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
     if verbose:
         print(res.stderr)
+    # the C driver links the library it sits beside (rpath $ORIGIN)
+    cli_cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17",
+               "-I", os.path.join(ROOT, "include"), os.path.join(PKG, "csrc", "tools", "nvfp4_gemm_cli.cu"),
+               "-L", PKG, "-lnvfp4_b200", "-Xlinker", "-rpath=$ORIGIN", "-o", CLI]
+    res = subprocess.run(cli_cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed on the C driver:\n" + res.stdout + res.stderr)
     return LIB
 
 

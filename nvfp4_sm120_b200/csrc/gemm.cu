@@ -52,11 +52,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   // that one wave of CTAs touches a near-square patch of A and B (both stay L2 resident)
   const uint32_t tiles_n = (uint32_t)((p.N + kTileN - 1) / kTileN), tiles_m = (uint32_t)((p.M + kTileM - 1) / kTileM);
   const uint32_t per_group = kGroupM * tiles_n;
-  const uint32_t group = blockIdx.x / per_group, first_m = group * kGroupM;
+  const uint32_t tile_id = blockIdx.x / (uint32_t)p.splits, split = blockIdx.x % (uint32_t)p.splits;
+  const uint32_t group = tile_id / per_group, first_m = group * kGroupM;
   const uint32_t gsize = min((uint32_t)kGroupM, tiles_m - first_m);
-  const uint32_t in_group = blockIdx.x - group * per_group;
+  const uint32_t in_group = tile_id - group * per_group;
   const int64_t m0 = (int64_t)(first_m + in_group % gsize) * kTileM, n0 = (int64_t)(in_group / gsize) * kTileN;
-  const int num_kt = (int)((p.K + kTileK - 1) / kTileK);
+  // this CTA's share of the K slices (all of them unless K is split)
+  const int total_kt = (int)((p.K + kTileK - 1) / kTileK);
+  const int per_split = (total_kt + p.splits - 1) / p.splits;
+  const int kt0 = (int)split * per_split;
+  const int num_kt = min(total_kt, kt0 + per_split) - kt0;
+  if (num_kt <= 0) return;                                       // whole CTA, before any barrier
   const int64_t sf_col_tiles = (p.K / 16 + 3) / 4;               // 512-byte tiles per 128-row group
 
   if (threadIdx.x == 0) {
@@ -87,15 +93,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           raise(abort_flag, p.status, kErrProducerWait);
           break;
         }
-        const int64_t k_left = p.K - (int64_t)kt * kTileK;
+        const int64_t k_left = p.K - (int64_t)(kt0 + kt) * kTileK;
         const int nkb = k_left >= kTileK ? 4 : (int)((k_left + 63) / 64);
         const uint32_t sf_bytes = (uint32_t)nkb * 512u;
         const uint32_t stage = base + s * kStageBytes;
         mbar_expect_tx(full_bar(s), kABytes + kBBytes + sf_bytes * (second_sfb ? 3u : 2u));
-        tma_load_2d(stage, &map_a, kt * 128, (int)m0, full_bar(s));
-        tma_load_2d(stage + kABytes, &map_b, kt * 128, (int)n0, full_bar(s));
-        const uint8_t* sfa = p.a_sf + ((m0 >> 7) * sf_col_tiles + (int64_t)kt * 4) * 512;
-        const uint8_t* sfb = p.b_sf + ((n0 >> 7) * sf_col_tiles + (int64_t)kt * 4) * 512;
+        tma_load_2d(stage, &map_a, (kt0 + kt) * 128, (int)m0, full_bar(s));
+        tma_load_2d(stage + kABytes, &map_b, (kt0 + kt) * 128, (int)n0, full_bar(s));
+        const uint8_t* sfa = p.a_sf + ((m0 >> 7) * sf_col_tiles + (int64_t)(kt0 + kt) * 4) * 512;
+        const uint8_t* sfb = p.b_sf + ((n0 >> 7) * sf_col_tiles + (int64_t)(kt0 + kt) * 4) * 512;
         bulk_load(stage + kABytes + kBBytes, sfa, sf_bytes, full_bar(s));
         bulk_load(stage + kABytes + kBBytes + kSfaBytes, sfb, sf_bytes, full_bar(s));
         if (second_sfb)
@@ -122,7 +128,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           break;
         }
         tc_fence_after();
-        const int64_t k_left = p.K - (int64_t)kt * kTileK;
+        const int64_t k_left = p.K - (int64_t)(kt0 + kt) * kTileK;
         const int nkb = k_left >= kTileK ? 4 : (int)((k_left + 63) / 64);
         const uint32_t stage = base + s * kStageBytes;
         const uint32_t t_sfa = tmem_sf0 + s * kSfColsPerStage, t_sfb = t_sfa + 16;
@@ -219,8 +225,8 @@ int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params
     attr_set[dev] = true;
   }
   const int64_t n_tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kTileM - 1) / kTileM);
-  if (n_tiles > 0x7fffffffLL) return NVFP4_E_SHAPE;
-  gemm_kernel<<<dim3((unsigned)n_tiles), kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  if (n_tiles * p.splits > 0x7fffffffLL) return NVFP4_E_SHAPE;
+  gemm_kernel<<<dim3((unsigned)(n_tiles * p.splits)), kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 }}  // namespace nvfp4::gemm

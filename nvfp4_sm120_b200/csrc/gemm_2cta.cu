@@ -300,6 +300,23 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
   CUtensorMap map_a, map_b;
   if (!make_operand_map(&map_a, a_q, M, K, 128) || !make_operand_map(&map_b, b_q, N, K, pair ? 128 : 256))
     return NVFP4_E_DRIVER;
-  Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status};
+  Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status, 1};
+  // Split K when a small fp32 output (the weight gradient: few tiles, K = tokens) would leave most SMs
+  // idle: the CTAs of a tile add their partial sums into the zeroed output.  Summation order then
+  // varies from run to run in the last bits, so it is used only where it pays: fewer tiles than half
+  // the SMs and at least 16 K slices.
+  if (!pair && p.out_f32) {
+    const int64_t tiles = ((N + 255) / 256) * ((M + 127) / 128), slices = (K + 255) / 256;
+    if (tiles <= 74 && slices >= 16) {
+      int64_t s = 148 / tiles;
+      if (s > slices / 4) s = slices / 4;              // at least 4 slices per CTA
+      if (s > 1) {
+        p.splits = (int)s;
+        cudaError_t e = (ldd == N) ? cudaMemsetAsync(d, 0, (size_t)M * N * 4, stream)
+                                   : cudaMemset2DAsync(d, (size_t)ldd * 4, 0, (size_t)N * 4, (size_t)M, stream);
+        if (e != cudaSuccess) return NVFP4_E_LAUNCH;
+      }
+    }
+  }
   return pair ? nvfp4::gemm2::launch_2cta(map_a, map_b, p, stream) : launch_1cta(map_a, map_b, p, stream);
 }

@@ -120,7 +120,8 @@ struct Params {
   int64_t M, N, K, ldd;
   int out_f32;
   int32_t* status;
-};
+  int splits;        // > 1: K is split over `splits` CTAs per tile, which add their partial sums into
+};                   // a zeroed fp32 output with atomics (one-CTA kernel only)
 
 __device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status, int code) {
   *abort_flag = 1;
@@ -133,6 +134,13 @@ __device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status,
 __device__ __forceinline__ void store_row_chunk(const Params& p, int64_t row, int64_t col, const uint32_t (&r)[32],
                                                 float alpha) {
   const bool full = (col + 32 <= p.N);
+  if (p.splits > 1) {                                   // split-K partial sum (fp32 output only)
+    float* out = static_cast<float*>(p.d) + row * p.ldd + col;
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (col + j < p.N) atomicAdd(out + j, __uint_as_float(r[j]) * alpha);
+    return;
+  }
   if (p.out_f32) {
     float* out = static_cast<float*>(p.d) + row * p.ldd + col;
     if (full && ((p.ldd & 3) == 0)) {

@@ -56,6 +56,22 @@ def test_two_cta_kernel_matches(Q, mnk):
     assert torch.allclose(one, two, rtol=1e-5, atol=1e-5 * ref.abs().max().item())
 
 
+@pytest.mark.parametrize("mnk", [(256, 256, 8192), (640, 512, 16384), (768, 3072, 4096)])
+def test_split_k_small_output(Q, mnk):
+    """Weight-gradient shapes (small fp32 output, long K): K is split over several CTAs per tile that
+    add into the zeroed output; same tolerance, and the bf16 path (never split) agrees."""
+    m, n, k = mnk
+    qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 14).cuda())
+    qb = Q.quant_nvfp4(O.synthetic_tensor(n, k, 15).cuda())
+    out = torch.full((m, n), 7.0, device="cuda")                 # stale contents must not leak in
+    got = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.float32, out=out).cpu()
+    assert Q.gemm_status() == 0
+    ref = _ref_from_gpu_quant(qa, qb, m, n, k)
+    assert ((got - ref).norm() / ref.norm()).item() < REL_TOL
+    bf = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.bfloat16).float().cpu()
+    assert ((bf - ref).norm() / ref.norm()).item() < 5e-3
+
+
 def test_gemm_bf16_out_is_rounded_fp32(Q):
     m, n, k = 256, 512, 1024
     qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 4).cuda())
@@ -130,3 +146,16 @@ def test_gemm_argument_errors(Q):
     with pytest.raises(ValueError):
         Q.nvfp4_mm(qa, qa)                           # right operand must be the .t() view
     assert _lib.lib().nvfp4_gemm(None, None, None, None, None, None, None, 0, 1, 1, 32, 1, None, None) == -1
+
+
+def test_standalone_c_driver_verifies():
+    """The C driver (no Python, no torch above the ABI) quantizes, multiplies and verifies on the host,
+    like the reference's CUTLASS executables (`--m --n --k --iterations --verify`, "Disposition: Passed")."""
+    import os
+    import subprocess
+    cli = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "nvfp4_sm120_b200", "nvfp4_gemm_cli")
+    assert os.path.exists(cli), "build with `python -m nvfp4_sm120_b200.build`"
+    for args in (["--m", "256", "--n", "512", "--k", "512"], ["--m", "1000", "--n", "776", "--k", "2048"]):
+        res = subprocess.run([cli] + args + ["--iterations", "3", "--verify"], capture_output=True, text=True, timeout=300)
+        assert res.returncode == 0, res.stdout + res.stderr
+        assert "Disposition: Passed" in res.stdout
