@@ -304,12 +304,12 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
   // Split K when a small fp32 output (the weight gradient: few tiles, K = tokens) would leave most SMs
   // idle: the CTAs of a tile add their partial sums into the zeroed output.  Summation order then
   // varies from run to run in the last bits, so it is used only where it pays: fewer tiles than half
-  // the SMs and at least 16 K slices.
+  // the SMs and at least 16 K slices (8 or more per CTA).
   if (!pair && p.out_f32) {
     const int64_t tiles = ((N + 255) / 256) * ((M + 127) / 128), slices = (K + 255) / 256;
     if (tiles <= 74 && slices >= 16) {
       int64_t s = 148 / tiles;
-      if (s > slices / 4) s = slices / 4;              // at least 4 slices per CTA
+      if (s > slices / 8) s = slices / 8;              // at least 8 slices per CTA
       if (s > 1) {
         p.splits = (int)s;
         cudaError_t e = (ldd == N) ? cudaMemsetAsync(d, 0, (size_t)M * N * 4, stream)

@@ -136,9 +136,17 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, int64_t row, in
   const bool full = (col + 32 <= p.N);
   if (p.splits > 1) {                                   // split-K partial sum (fp32 output only)
     float* out = static_cast<float*>(p.d) + row * p.ldd + col;
+    if (full && ((p.ldd & 3) == 0)) {                   // four floats per reduction instruction
 #pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (col + j < p.N) atomicAdd(out + j, __uint_as_float(r[j]) * alpha);
+      for (int j = 0; j < 32; j += 4)
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                     ::"l"(out + j), "f"(__uint_as_float(r[j]) * alpha), "f"(__uint_as_float(r[j + 1]) * alpha),
+                       "f"(__uint_as_float(r[j + 2]) * alpha), "f"(__uint_as_float(r[j + 3]) * alpha) : "memory");
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col + j < p.N) atomicAdd(out + j, __uint_as_float(r[j]) * alpha);
+    }
     return;
   }
   if (p.out_f32) {
