@@ -120,25 +120,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc(kTileM, kTileN);
       bool ok = true;
-      for (int kt = 0; kt < num_kt && ok; ++kt) {
-        const int s = kt % kStages;
-        if (!mbar_wait(sf_bar(s), (kt / kStages) & 1, abort_flag)) {     // implies the TMA data landed
+      // K slices that hold all four K=64 blocks (every one except possibly the last of the matrix)
+      const int whole_kt = (int)min((int64_t)num_kt, max((int64_t)0, p.K / kTileK - kt0));
+      int s = 0;
+      uint32_t parity = 0;
+      for (int kt = 0; kt < num_kt; ++kt) {
+        if (!mbar_wait(sf_bar(s), parity, abort_flag)) {                 // implies the TMA data landed
           raise(abort_flag, p.status, kErrMmaWait);
           ok = false;
           break;
         }
         tc_fence_after();
-        const int64_t k_left = p.K - (int64_t)(kt0 + kt) * kTileK;
-        const int nkb = k_left >= kTileK ? 4 : (int)((k_left + 63) / 64);
         const uint32_t stage = base + s * kStageBytes;
         const uint32_t t_sfa = tmem_sf0 + s * kSfColsPerStage, t_sfb = t_sfa + 16;
         const uint64_t da = make_desc_sw128(stage), db = make_desc_sw128(stage + kABytes);
-        for (int kb = 0; kb < nkb; ++kb) {
-          // 64 elements = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
-          tc_mma_nvf4(tmem_base, da + 2u * kb, db + 2u * kb, idesc, t_sfa + 4 * kb, t_sfb + 8 * kb,
-                      (kt > 0 || kb > 0) ? 1u : 0u);
+        // 64 elements = 32 bytes further along K inside the swizzled row: +2 in 16-byte units.
+        // The four instructions go out back to back: the tensor pipe only stays busy while the next
+        // one is already queued, so nothing else sits between them.
+        if (kt < whole_kt) {
+          tc_mma_nvf4(tmem_base, da, db, idesc, t_sfa, t_sfb, kt > 0 ? 1u : 0u);
+          tc_mma_nvf4(tmem_base, da + 2u, db + 2u, idesc, t_sfa + 4, t_sfb + 8, 1u);
+          tc_mma_nvf4(tmem_base, da + 4u, db + 4u, idesc, t_sfa + 8, t_sfb + 16, 1u);
+          tc_mma_nvf4(tmem_base, da + 6u, db + 6u, idesc, t_sfa + 12, t_sfb + 24, 1u);
+        } else {
+          const int nkb = (int)((p.K - (int64_t)(kt0 + kt) * kTileK + 63) / 64);
+          for (int kb = 0; kb < nkb; ++kb)
+            tc_mma_nvf4(tmem_base, da + 2u * kb, db + 2u * kb, idesc, t_sfa + 4 * kb, t_sfb + 8 * kb,
+                        (kt > 0 || kb > 0) ? 1u : 0u);
         }
         tc_commit(empty_bar(s));          // frees the stage once these MMAs have read it
+        if (++s == kStages) { s = 0; parity ^= 1u; }
       }
       if (ok) tc_commit(acc_bar);         // accumulator complete
     }

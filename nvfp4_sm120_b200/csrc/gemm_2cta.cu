@@ -164,25 +164,36 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     if (lane == 0 && leader) {
       constexpr uint32_t idesc = make_idesc(256, kTileN);
       bool ok = true;
-      for (int kt = 0; kt < num_kt && ok; ++kt) {
-        const int s = kt % kStages;
-        const uint32_t par = (kt / kStages) & 1;
-        if (!mbar_wait(full_bar(s), par, abort_flag) || !mbar_wait(sready_bar(s), par, abort_flag)) {
+      const int whole_kt = (int)min((int64_t)num_kt, p.K / kTileK);     // K slices with all four K=64 blocks
+      const uint32_t partner_empty0 = map_to_cta(empty_bar(0), 1);
+      int s = 0;
+      uint32_t par = 0;
+      for (int kt = 0; kt < num_kt; ++kt) {
+        // one wait per K slice: the leader's scale warps arrive only after the operand tiles of both
+        // CTAs have landed, so "scales ready" covers "data landed"
+        if (!mbar_wait(sready_bar(s), par, abort_flag)) {
           raise(abort_flag, p.status, kErrMmaWait);
           ok = false;
           break;
         }
         tc_fence_after();
-        const int64_t k_left = p.K - (int64_t)kt * kTileK;
-        const int nkb = k_left >= kTileK ? 4 : (int)((k_left + 63) / 64);
         const uint32_t stage = base + s * kStageBytes;
         const uint32_t t_sfa = tmem_sf0 + s * kSfColsPerStage, t_sfb = t_sfa + 16;
         const uint64_t da = make_desc_sw128(stage), db = make_desc_sw128(stage + kABytes);
-        for (int kb = 0; kb < nkb; ++kb)
-          tc_mma_nvf4_pair(tmem_base, da + 2u * kb, db + 2u * kb, idesc, t_sfa + 4 * kb, t_sfb + 8 * kb,
-                           (kt > 0 || kb > 0) ? 1u : 0u);
+        if (kt < whole_kt) {                                  // back to back, nothing in between
+          tc_mma_nvf4_pair(tmem_base, da, db, idesc, t_sfa, t_sfb, kt > 0 ? 1u : 0u);
+          tc_mma_nvf4_pair(tmem_base, da + 2u, db + 2u, idesc, t_sfa + 4, t_sfb + 8, 1u);
+          tc_mma_nvf4_pair(tmem_base, da + 4u, db + 4u, idesc, t_sfa + 8, t_sfb + 16, 1u);
+          tc_mma_nvf4_pair(tmem_base, da + 6u, db + 6u, idesc, t_sfa + 12, t_sfb + 24, 1u);
+        } else {
+          const int nkb = (int)((p.K - (int64_t)kt * kTileK + 63) / 64);
+          for (int kb = 0; kb < nkb; ++kb)
+            tc_mma_nvf4_pair(tmem_base, da + 2u * kb, db + 2u * kb, idesc, t_sfa + 4 * kb, t_sfb + 8 * kb,
+                             (kt > 0 || kb > 0) ? 1u : 0u);
+        }
         tc_commit_pair(empty_bar(s));                       // frees the stage here ...
-        tc_commit_pair(map_to_cta(empty_bar(s), 1));        // ... and in the partner CTA
+        tc_commit_pair(partner_empty0 + 8u * s);            // ... and in the partner CTA
+        if (++s == kStages) { s = 0; par ^= 1u; }
       }
       if (ok) {
         tc_commit_pair(acc_bar);
@@ -197,7 +208,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const uint32_t leader_ready0 = map_to_cta(sready_bar(0), 0);
     for (int kt = set; kt < num_kt && ok; kt += 2) {
       const int s = kt % kStages;
-      if (lane == 0) ok = mbar_wait(sfull_bar(s), (kt / kStages) & 1, abort_flag);
+      if (lane == 0) {
+        ok = mbar_wait(sfull_bar(s), (kt / kStages) & 1, abort_flag);
+        if (ok && leader) ok = mbar_wait(full_bar(s), (kt / kStages) & 1, abort_flag);   // see the MMA issuer
+      }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) { if (lane == 0) raise(abort_flag, p.status, kErrScaleWait); break; }
       const uint8_t* sf_s = smem + s * kStageBytes + kABytes + kBBytes + lane * 16;
