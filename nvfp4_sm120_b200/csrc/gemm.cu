@@ -33,7 +33,8 @@ constexpr int kThreads = 192;
 constexpr int kSfColsPerStage = 16 + 32;    // SFA 4 columns per K=64 block, SFB 8
 
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_d, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;                 // 1024-byte alignment for the swizzle
@@ -203,13 +204,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const float alpha = __ldg(p.a_pts) * __ldg(p.b_pts);
       const int64_t row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      if (p.tma_store) {
+        // every MMA has finished and every TMA load has landed, so the stages are free: 32 KiB per warp
+        drain_through_tma(p, &map_d, taddr, smem + (warp - 2) * 32768, m0 + quad * 32, n0, 0, kTileN, alpha, lane);
+      } else {
 #pragma unroll 1
-      for (int c0 = 0; c0 < kTileN; c0 += 32) {
-        if (n0 + c0 >= p.N) break;                               // uniform across the warp
-        uint32_t r[32];
-        tc_ld_32x32b_x32(taddr + c0, r);
-        tc_wait_ld();
-        if (row < p.M) store_row_chunk(p, row, n0 + c0, r, alpha);
+        for (int c0 = 0; c0 < kTileN; c0 += 32) {
+          if (n0 + c0 >= p.N) break;                             // uniform across the warp
+          uint32_t r[32];
+          tc_ld_32x32b_x32(taddr + c0, r);
+          tc_wait_ld();
+          if (row < p.M) store_row_chunk(p, row, n0 + c0, r, alpha);
+        }
       }
     }
   }
@@ -226,7 +232,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
 namespace nvfp4 { namespace gemm {
 // launch of the one-CTA kernel (arguments already validated)
-int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream) {
+int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const Params& p,
+                cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
@@ -237,7 +244,7 @@ int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params
   }
   const int64_t n_tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kTileM - 1) / kTileM);
   if (n_tiles * p.splits > 0x7fffffffLL) return NVFP4_E_SHAPE;
-  gemm_kernel<<<dim3((unsigned)(n_tiles * p.splits)), kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  gemm_kernel<<<dim3((unsigned)(n_tiles * p.splits)), kThreads, kSmemBytes, stream>>>(map_a, map_b, map_d, p);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 }}  // namespace nvfp4::gemm

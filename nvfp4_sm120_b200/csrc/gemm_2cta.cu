@@ -73,7 +73,8 @@ __device__ __forceinline__ void tc_mma_nvf4_pair(uint32_t tmem_d, uint64_t desc_
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+             const __grid_constant__ CUtensorMap map_d, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;                 // same offset in both CTAs of the pair
@@ -248,13 +249,19 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       const float alpha = __ldg(p.a_pts) * __ldg(p.b_pts);
       const int64_t row = m0 + quad * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      if (p.tma_store) {
+        // every MMA of the pair has finished and every load has landed: the stages are free, 16 KiB per warp
+        drain_through_tma(p, &map_d, taddr, smem + (warp - 2) * 16384, m0 + quad * 32, n0, 128 * set, 128 * set + 128,
+                          alpha, lane);
+      } else {
 #pragma unroll 1
-      for (int c0 = 128 * set; c0 < 128 * set + 128; c0 += 32) {     // each set drains half of the columns
-        if (n0 + c0 >= p.N) break;
-        uint32_t r[32];
-        tc_ld_32x32b_x32(taddr + c0, r);
-        tc_wait_ld();
-        if (row < p.M) store_row_chunk(p, row, n0 + c0, r, alpha);
+        for (int c0 = 128 * set; c0 < 128 * set + 128; c0 += 32) {   // each set drains half of the columns
+          if (n0 + c0 >= p.N) break;
+          uint32_t r[32];
+          tc_ld_32x32b_x32(taddr + c0, r);
+          tc_wait_ld();
+          if (row < p.M) store_row_chunk(p, row, n0 + c0, r, alpha);
+        }
       }
     }
   }
@@ -267,7 +274,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
   }
 }
 
-int launch_2cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream) {
+int launch_2cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const Params& p,
+                cudaStream_t stream) {
   static bool attr_set[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
@@ -278,27 +286,32 @@ int launch_2cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params
   }
   const int64_t n_ctas = 2 * ((p.N + kTileN - 1) / kTileN) * ((p.M + 255) / 256);
   if (n_ctas > 0x7fffffffLL) return NVFP4_E_SHAPE;
-  gemm2_kernel<<<dim3((unsigned)n_ctas), kThreads, kSmemBytes, stream>>>(map_a, map_b, p);
+  gemm2_kernel<<<dim3((unsigned)n_ctas), kThreads, kSmemBytes, stream>>>(map_a, map_b, map_d, p);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 
 }  // namespace gemm2
 }  // namespace nvfp4
 
+namespace nvfp4 { namespace gemm3 {
+int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const gemm::Params& p,
+                cudaStream_t stream);
+}}
 namespace nvfp4 { namespace gemm {
-int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, cudaStream_t stream);
+int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const Params& p,
+                cudaStream_t stream);
 }}
 
 static int g_gemm_mode = 0;
 extern "C" int nvfp4_gemm_set_mode(int mode) {
-  if (mode < 0 || mode > 2) return NVFP4_E_MODE;
+  if (mode < 0 || mode > 3) return NVFP4_E_MODE;
   g_gemm_mode = mode;
   return NVFP4_OK;
 }
 
-// Automatic choice: the one-CTA kernel.  Measured on B200 it is as fast or faster than the paired
-// kernel on every shape tried (both top out near 180-200 cycles per K=64 MMA step), and it wastes
-// nothing when M is not a multiple of 256; the paired kernel stays selectable (mode 2) and tested.
+// Automatic choice: the persistent pair kernel (mode 3), which measured fastest on every shape with
+// more than one row tile; the one-CTA kernel when M <= 128 (a pair would compute 128 rows of padding)
+// and for the split-K case below.  Modes 1-3 force a kernel, for tuning and tests.
 extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
                           const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
                           int64_t K, int64_t ldd, int32_t* status, void* stream_) {
@@ -310,19 +323,22 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
   if (out_dtype != NVFP4_OUT_BF16 && out_dtype != NVFP4_OUT_F32) return NVFP4_E_MODE;
   auto mis = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
   if (mis(a_q, 16) || mis(b_q, 16) || mis(a_sf, 16) || mis(b_sf, 16) || mis(d, 16)) return NVFP4_E_ALIGN;
-  const bool pair = g_gemm_mode == 2;
+  // split K (one-CTA kernel only, see below) when a small fp32 output would leave most SMs idle
+  const int64_t tiles_1cta = ((N + 255) / 256) * ((M + 127) / 128), slices = (K + 255) / 256;
+  const bool want_split = out_dtype == NVFP4_OUT_F32 && tiles_1cta <= 74 && slices >= 16;
+  const int mode = g_gemm_mode != 0 ? g_gemm_mode : ((M > 128 && !want_split) ? 3 : 1);
+  const bool pair = mode >= 2;
   CUtensorMap map_a, map_b;
   if (!make_operand_map(&map_a, a_q, M, K, 128) || !make_operand_map(&map_b, b_q, N, K, pair ? 128 : 256))
     return NVFP4_E_DRIVER;
-  Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status, 1};
+  Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status, 1, 0};
   // Split K when a small fp32 output (the weight gradient: few tiles, K = tokens) would leave most SMs
   // idle: the CTAs of a tile add their partial sums into the zeroed output.  Summation order then
   // varies from run to run in the last bits, so it is used only where it pays: fewer tiles than half
   // the SMs and at least 16 K slices (8 or more per CTA).
-  if (!pair && p.out_f32) {
-    const int64_t tiles = ((N + 255) / 256) * ((M + 127) / 128), slices = (K + 255) / 256;
-    if (tiles <= 74 && slices >= 16) {
-      int64_t s = 148 / tiles;
+  if (!pair && want_split) {
+    {
+      int64_t s = 148 / tiles_1cta;
       if (s > slices / 8) s = slices / 8;              // at least 8 slices per CTA
       if (s > 1) {
         p.splits = (int)s;
@@ -332,5 +348,13 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
       }
     }
   }
-  return pair ? nvfp4::gemm2::launch_2cta(map_a, map_b, p, stream) : launch_1cta(map_a, map_b, p, stream);
+  // The epilogue stores through TMA when the row pitch allows a tensor map (a multiple of 16 bytes)
+  // and the output is written, not accumulated into.
+  CUtensorMap map_d = map_a;                                   // placeholder when unused
+  if (p.splits == 1 && (ldd * (p.out_f32 ? 4 : 2)) % 16 == 0) {
+    if (!make_output_map(&map_d, d, M, N, ldd, p.out_f32 != 0)) return NVFP4_E_DRIVER;
+    p.tma_store = 1;
+  }
+  if (mode == 3) return nvfp4::gemm3::launch_pair(map_a, map_b, map_d, p, stream);
+  return pair ? nvfp4::gemm2::launch_2cta(map_a, map_b, map_d, p, stream) : launch_1cta(map_a, map_b, map_d, p, stream);
 }

@@ -121,7 +121,9 @@ struct Params {
   int out_f32;
   int32_t* status;
   int splits;        // > 1: K is split over `splits` CTAs per tile, which add their partial sums into
-};                   // a zeroed fp32 output with atomics (one-CTA kernel only)
+                     // a zeroed fp32 output with atomics (one-CTA kernel only)
+  int tma_store;     // the output goes through shared memory and TMA stores (needs a 16-byte row pitch)
+};
 
 __device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status, int code) {
   *abort_flag = 1;
@@ -184,6 +186,69 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, int64_t row, in
   }
 }
 
+
+// ---- epilogue through shared memory and TMA stores -------------------------------------------
+// A lane owns one accumulator row, so direct stores touch 32 different rows per instruction and the
+// load/store unit spends one cycle per 32-byte sector.  Instead each warp lays 32 rows x 128 bytes
+// out in shared memory in the 128-byte swizzle (conflict-free: the eight lanes of a quarter warp hit
+// eight different 16-byte slots) and one lane hands the box to the TMA unit, which writes whole
+// lines and clips at the matrix edge.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(x), "r"(y), "r"(src) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Drains accumulator columns [c_begin, c_end) (multiples of 64) of this warp's 32 TMEM lanes =
+// output rows row0 .. row0 + 31.  `buf` is this warp's staging area: 4 KiB per box, a box being 64
+// bf16 or 32 fp32 columns, 1024-byte aligned, not reused (so nothing waits until the end).
+__device__ __forceinline__ void drain_through_tma(const Params& p, const CUtensorMap* map_d, uint32_t taddr,
+                                                  uint8_t* buf, int64_t row0, int64_t n0, int c_begin, int c_end,
+                                                  float alpha, int lane) {
+  if (row0 >= p.M) return;                               // padded rows of a pair: nothing to write
+  const uint32_t sw = (uint32_t)lane & 7u;
+  int box = 0;
+#pragma unroll 1
+  for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+    if (n0 + c0 >= p.N) break;                           // uniform across the warp
+    uint32_t r[32];
+    tc_ld_32x32b_x32(taddr + c0, r);
+    tc_wait_ld();
+    uint8_t* rowp = buf + box * 4096 + lane * 128;
+    bool box_done = true;
+    int x = (int)(n0 + c0);
+    if (p.out_f32) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<float4*>(rowp + (((uint32_t)j ^ sw) << 4)) =
+            make_float4(__uint_as_float(r[4 * j]) * alpha, __uint_as_float(r[4 * j + 1]) * alpha,
+                        __uint_as_float(r[4 * j + 2]) * alpha, __uint_as_float(r[4 * j + 3]) * alpha);
+    } else {
+      const int half = ((c0 - c_begin) >> 5) & 1;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * q]) * alpha,
+                                                   __uint_as_float(r[8 * j + 2 * q + 1]) * alpha);
+          w[q] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(rowp + (((uint32_t)(4 * half + j) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      box_done = half == 1 || c0 + 32 >= c_end || n0 + c0 + 32 >= p.N;
+      x -= 32 * half;
+    }
+    if (box_done) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> TMA reads
+      __syncwarp();
+      if (lane == 0) tma_store_2d(map_d, smem_u32(buf + box * 4096), x, (int)row0);
+      ++box;
+    }
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // before shared memory goes away
+  __syncwarp();
+}
+
 // ---- host side ------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -213,6 +278,21 @@ inline bool make_operand_map(CUtensorMap* map, const uint8_t* ptr, int64_t rows,
   cuuint32_t estr[2] = {1u, 1u};
   return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(ptr), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+
+// row-major output [M, ldd] -> 2-D tensor map for the epilogue's stores: boxes of 32 rows x 128 bytes
+inline bool make_output_map(CUtensorMap* map, void* d, int64_t M, int64_t N, int64_t ldd, bool f32) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t elem = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)ldd * elem};
+  cuuint32_t box[2] = {f32 ? 32u : 64u, 32u};
+  cuuint32_t estr[2] = {1u, 1u};
+  return fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, d, dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 

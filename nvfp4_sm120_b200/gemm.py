@@ -34,6 +34,10 @@ def nvfp4_mm(a: NVFP4Tensor, b: NVFP4Tensor, out_dtype=None, out=None) -> torch.
     n, k2b = b.qdata.shape
     if k2 != k2b:
         raise ValueError(f"contraction mismatch: {k2 * 2} vs {k2b * 2}")
+    if out is not None:
+        if tuple(out.shape) != (m, n) or out.stride(1) != 1 or (out_dtype is not None and out.dtype != out_dtype):
+            raise ValueError("out must be [M, N] with unit column stride and the requested dtype")
+        out_dtype = out.dtype
     if out_dtype is None:
         out_dtype = torch.float32 if a.orig_dtype == torch.float32 else torch.bfloat16
     if out_dtype not in (torch.bfloat16, torch.float32):

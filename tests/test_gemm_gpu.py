@@ -36,9 +36,11 @@ def test_gemm_fp32_out_matches_dequant_matmul(Q, mnk):
     assert torch.allclose(got, ref, rtol=2e-3, atol=2e-3 * ref.abs().max().item())
 
 
+@pytest.mark.parametrize("mode", [2, 3])
 @pytest.mark.parametrize("mnk", [(256, 512, 512), (130, 200, 320), (384, 768, 2048), (48, 80, 64), (1024, 1024, 4096)])
-def test_two_cta_kernel_matches(Q, mnk):
-    """The cta_group::2 kernel (mode 2) gives the one-CTA kernel's result and meets the tolerance."""
+def test_two_cta_kernel_matches(Q, mnk, mode):
+    """The cta_group::2 kernels (mode 2: one tile per cluster; mode 3: persistent) give the one-CTA
+    kernel's result and meet the tolerance, in fp32 and in bf16."""
     from nvfp4_sm120_b200 import _lib
     m, n, k = mnk
     qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 12).cuda())
@@ -46,14 +48,45 @@ def test_two_cta_kernel_matches(Q, mnk):
     try:
         _lib.lib().nvfp4_gemm_set_mode(1)
         one = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.float32).cpu()
-        _lib.lib().nvfp4_gemm_set_mode(2)
+        one_bf = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.bfloat16).cpu()
+        _lib.lib().nvfp4_gemm_set_mode(mode)
         two = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.float32).cpu()
+        two_bf = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.bfloat16).cpu()
     finally:
         _lib.lib().nvfp4_gemm_set_mode(0)
     assert Q.gemm_status() == 0
     ref = _ref_from_gpu_quant(qa, qb, m, n, k)
     assert ((two - ref).norm() / ref.norm()).item() < REL_TOL
     assert torch.allclose(one, two, rtol=1e-5, atol=1e-5 * ref.abs().max().item())
+    assert torch.equal(two_bf, two.to(torch.bfloat16))              # same accumulation, rounded once
+    # the one-CTA fp32 result may come from the split-K path (another summation order): one bf16 ulp
+    assert torch.allclose(one_bf.float(), one, rtol=2.0 ** -7, atol=1e-5 * ref.abs().max().item())
+
+
+@pytest.mark.parametrize("mode", [1, 2, 3])
+def test_many_tiles_per_cluster_and_strided_output(Q, mode):
+    """More tiles than SM pairs (the persistent kernel loops), ragged M and N, and an output whose
+    row pitch is larger than N (TMA-store epilogue with a pitch) or not a multiple of 16 bytes
+    (direct stores)."""
+    from nvfp4_sm120_b200 import _lib
+    m, n, k = 2500, 2100, 512
+    qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 21).cuda())
+    qb = Q.quant_nvfp4(O.synthetic_tensor(n, k, 22).cuda())
+    ref = _ref_from_gpu_quant(qa, qb, m, n, k)
+    try:
+        _lib.lib().nvfp4_gemm_set_mode(mode)
+        for dtype in (torch.float32, torch.bfloat16):
+            for pitch in (n, n + 8, n + 3):
+                buf = torch.full((m, pitch), 7.0, device="cuda", dtype=dtype)
+                Q.nvfp4_mm(qa, qb.t(), out=buf[:, :n])
+                got = buf[:, :n].float().cpu()
+                tol = REL_TOL if dtype == torch.float32 else 4e-3
+                assert ((got - ref).norm() / ref.norm()).item() < tol, (mode, dtype, pitch)
+                if pitch > n:
+                    assert bool((buf[:, n:] == 7.0).all()), "wrote past column N"
+    finally:
+        _lib.lib().nvfp4_gemm_set_mode(0)
+    assert Q.gemm_status() == 0
 
 
 @pytest.mark.parametrize("mnk", [(256, 256, 8192), (640, 512, 16384), (768, 3072, 4096)])
