@@ -8,7 +8,7 @@
 //   warp 1      (leader CTA only) issues tcgen05.mma cta_group::2, M 256 = 128 per CTA, N 256, K 64:
 //               four per K slice, back to back, one barrier wait per slice;
 //   warps 2-9   two sets of four: scale factors shared memory -> registers -> tensor memory;
-//   warps 10-13 epilogue: tensor memory -> registers -> swizzled shared memory -> TMA store.
+//   warps 10-17 epilogue: tensor memory -> registers -> swizzled shared memory -> TMA store.
 // Because the ring never drains, the loads of the next tile are in flight while the epilogue warps
 // empty the accumulator; the MMA issuer only waits for "accumulator read" before the next tile, so
 // the launch, barrier set-up, tensor-memory allocation and pipeline fill are paid once per SM pair,
@@ -28,9 +28,11 @@ constexpr int kBBytes = 128 * 128;          // this CTA's 128 of the 256 B rows
 constexpr int kSfaBytes = 4 * 512;
 constexpr int kSfbBytes = 2 * 4 * 512;
 constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;      // 38912
-constexpr int kOutBytes = 4 * 2 * 4096;     // per epilogue warp two boxes of 32 rows x 128 bytes
+constexpr int kOutBytes = 8 * 4096;         // per epilogue warp one box of 32 rows x 128 bytes
 constexpr int kSmemBytes = kStages * kStageBytes + kOutBytes + 1024 + 256;
-constexpr int kThreads = 14 * 32;
+constexpr int kSfSets = 1;                  // groups of four scale-factor warps taking the K slices in turn
+constexpr int kEpiWarp0 = 2 + 4 * kSfSets;  // first epilogue warp
+constexpr int kThreads = (kEpiWarp0 + 8) * 32;
 constexpr int kSfColsPerStage = 48;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -120,7 +122,7 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(sfull_bar(s), 1); mbar_init(sready_bar(s), 8);
     }
     mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 8);
+    mbar_init(acc_empty, 16);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -236,7 +238,7 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
         }
       }
     }
-  } else if (warp < 10) {
+  } else if (warp < kEpiWarp0) {
     // ------------------------------ scale factors ------------------------------
     // Lane l / 32-bit column c of a K=64 block must hold, in every 32-lane quarter of tensor memory,
     // the four E4M3 scales of row 32c + l: exactly 16 bytes per lane of the 512-byte tile the
@@ -247,7 +249,7 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const uint32_t leader_ready0 = map_to_cta(sready_bar(0), 0);
     const int64_t total_g = (int64_t)my_tiles * num_kt;
     bool ok = true;
-    for (int64_t g = set; g < total_g && ok; g += 2) {
+    for (int64_t g = set; g < total_g && ok; g += kSfSets) {
       const int s = (int)(g % kStages);
       const uint32_t par = (uint32_t)(g / kStages) & 1u;
       if (lane == 0) {
@@ -282,80 +284,98 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     }
   } else {
     // ------------------------------ epilogue ------------------------------
-    // One warp per 32-lane quarter of tensor memory: 32 output rows x 256 columns per tile, 32
-    // columns at a time -> registers -> a swizzled 32 x 128-byte box in shared memory -> TMA store
-    // (two boxes per warp in turn).  "Accumulator read" is signalled right after the last
-    // tensor-memory load, before its conversion and store.
+    // Two warps per 32-lane quarter of tensor memory, 128 accumulator columns each.  For bf16 output a
+    // warp pulls its 32 x 128 slab into registers as packed bf16 (64 registers), signals "accumulator
+    // read" -- the MMA issuer starts the next tile about 600 cycles after the last MMA of this one --
+    // and only then writes the slab out at leisure, under the next tile's main loop: swizzled
+    // 32 x 128-byte box in shared memory -> TMA store, which writes whole lines and clips at the
+    // matrix edge.  fp32 output (128 registers would not fit) goes box by box and signals after its
+    // last tensor-memory load.
     const int quad = warp & 3;
-    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    uint8_t* buf = out_stage + (warp - 10) * 8192;
+    const int c_base = 128 * ((warp - kEpiWarp0) >> 2);
+    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + c_base;
+    uint8_t* box = out_stage + (warp - kEpiWarp0) * 4096;
+    const uint32_t box_u32 = smem_u32(box);
+    uint8_t* rowp = box + lane * 128;
     const uint32_t leader_acc_empty = map_to_cta(acc_empty, 0);
     const float alpha = __ldg(p.a_pts) * __ldg(p.b_pts);
     const uint32_t sw = (uint32_t)lane & 7u;
-    uint32_t boxes = 0;                                           // boxes handed to the TMA unit so far
     bool ok = true;
+    auto release_accumulator = [&]() {
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { if (leader) mbar_arrive(acc_empty); else mbar_arrive_cluster(leader_acc_empty); }
+    };
+    auto send_box = [&](int64_t x, int64_t y) {                   // the box is written: hand it to the TMA unit
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> TMA reads
+      __syncwarp();
+      if (lane == 0) tma_store_2d(&map_d, box_u32, (int)x, (int)y);
+    };
+    auto box_free = [&]() {                                       // its last store has read the box
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      __syncwarp();
+    };
     for (int i = 0; i < my_tiles; ++i) {
       int64_t pair_m0, n0;
       tm.locate(cluster_id + (uint32_t)i * n_clusters, pair_m0, n0);
       const int64_t row0 = pair_m0 + (int64_t)rank * 128 + quad * 32;
-      if (lane == 0) ok = mbar_wait(acc_full, (uint32_t)i & 1u, abort_flag);
+      const int64_t col0 = n0 + c_base;
+      if (lane == 0) ok = mbar_wait_relaxed(acc_full, (uint32_t)i & 1u, abort_flag);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) { if (lane == 0) raise(abort_flag, p.status, kErrEpilogueWait); break; }
       tc_fence_after();
-      const int64_t n_left = p.N - n0;
-      const int chunks = row0 >= p.M ? 0 : (n_left >= kTileN ? kTileN / 32 : (int)((n_left + 31) / 32));
-      auto release_accumulator = [&]() {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) { if (leader) mbar_arrive(acc_empty); else mbar_arrive_cluster(leader_acc_empty); }
-      };
-      if (chunks == 0) release_accumulator();
+      if (row0 >= p.M || col0 >= p.N) {                           // padding only: nothing to read
+        release_accumulator();
+        continue;
+      }
+      if (p.tma_store && !p.out_f32) {
+        uint32_t packed[64];
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t r[32];
+          tc_ld_32x32b_x32(taddr + 32 * ch, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 16; ++q) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * q]) * alpha, __uint_as_float(r[2 * q + 1]) * alpha);
+            packed[16 * ch + q] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        release_accumulator();
+#pragma unroll
+        for (int b = 0; b < 2; ++b) {
+          if (col0 + 64 * b >= p.N) break;                        // uniform across the warp
+          box_free();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(rowp + (((uint32_t)j ^ sw) << 4)) =
+                make_uint4(packed[32 * b + 4 * j], packed[32 * b + 4 * j + 1], packed[32 * b + 4 * j + 2], packed[32 * b + 4 * j + 3]);
+          send_box(col0 + 64 * b, row0);
+        }
+      } else {
+        const int64_t n_left = p.N - col0;
+        const int chunks = n_left >= 128 ? 4 : (int)((n_left + 31) / 32);
 #pragma unroll 1
-      for (int ch = 0; ch < chunks; ++ch) {
-        const int c0 = 32 * ch;
-        uint32_t r[32];
-        tc_ld_32x32b_x32(taddr + c0, r);
-        tc_wait_ld();
-        if (ch == chunks - 1) release_accumulator();
-        if (!p.tma_store) {
-          if (row0 + lane < p.M) store_row_chunk(p, row0 + lane, n0 + c0, r, alpha);
-          continue;
-        }
-        const int half = p.out_f32 ? 0 : (ch & 1);
-        if (half == 0) {                                          // a new box: its last store must have read it
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-        }
-        uint8_t* rowp = buf + (boxes & 1u) * 4096 + lane * 128;
-        if (p.out_f32) {
+        for (int ch = 0; ch < chunks; ++ch) {
+          uint32_t r[32];
+          tc_ld_32x32b_x32(taddr + 32 * ch, r);
+          tc_wait_ld();
+          if (ch == chunks - 1) release_accumulator();
+          if (!p.tma_store) {
+            if (row0 + lane < p.M) store_row_chunk(p, row0 + lane, col0 + 32 * ch, r, alpha);
+            continue;
+          }
+          box_free();                                             // fp32: a box is 32 columns
 #pragma unroll
           for (int j = 0; j < 8; ++j)
             *reinterpret_cast<float4*>(rowp + (((uint32_t)j ^ sw) << 4)) =
                 make_float4(__uint_as_float(r[4 * j]) * alpha, __uint_as_float(r[4 * j + 1]) * alpha,
                             __uint_as_float(r[4 * j + 2]) * alpha, __uint_as_float(r[4 * j + 3]) * alpha);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint32_t w[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * j + 2 * q]) * alpha,
-                                                       __uint_as_float(r[8 * j + 2 * q + 1]) * alpha);
-              w[q] = *reinterpret_cast<uint32_t*>(&h);
-            }
-            *reinterpret_cast<uint4*>(rowp + (((uint32_t)(4 * half + j) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        }
-        if (p.out_f32 || half == 1 || ch == chunks - 1) {
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> TMA reads
-          __syncwarp();
-          if (lane == 0) tma_store_2d(&map_d, smem_u32(buf + (boxes & 1u) * 4096), (int)(n0 + c0 - 32 * half), (int)row0);
-          ++boxes;
+          send_box(col0 + 32 * ch, row0);
         }
       }
     }
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // before shared memory goes away
-    __syncwarp();
+    box_free();                                                   // before shared memory goes away
   }
   tc_fence_before();
   __syncthreads();
