@@ -1,9 +1,11 @@
 // Two-CTA block-scaled NVFP4 GEMM for B200 (sm_100a): a pair of CTAs on neighbouring SMs (a
 // cluster of 2) computes one 256 x 256 output tile with tcgen05.mma cta_group::2.
 //
-// Why pairs: a one-CTA 128 x 256 MMA has to read 4 KiB of A and 8 KiB of B from shared memory per
-// K=64 step and runs at about 65 % of the tensor-core rate (measured); in a pair each CTA holds only
-// half of the B rows (4 KiB per step), which the shared-memory port sustains at full rate.
+// Why pairs: per K slice of 256 a one-CTA 128 x 256 tile has to bring 48 KiB of operands from the L2
+// into shared memory for 512 cycles of MMA work, and the L2 -> SM path delivers about 64 bytes per
+// clock; in a pair each CTA holds only half of the B rows (32 KiB per slice for the same flops).
+// This file is the one-tile-per-cluster form; gemm_pair.cu is the persistent form of the same
+// kernel, which nvfp4_gemm picks by default.
 //
 // Per CTA (rank r in the pair) and K slice of 256 elements:
 //   TMA tensor copies: A rows [m0 + 128 r, +128), B rows [n0 + 128 r, +128)  -> 128B-swizzled smem,

@@ -2,6 +2,7 @@
 
     python -m nvfp4_sm120_b200.profile_case quant --rows 16384 --cols 8192 --mode rht_sr --iters 3
     python -m nvfp4_sm120_b200.profile_case gemm --m 4096 --n 4096 --k 4096 --iters 3
+    python -m nvfp4_sm120_b200.profile_case block --d 768 --heads 12 --tokens 16384 --iters 3
 
 Prints the CUDA-event time per iteration.  Inputs are random bf16 from a device generator."""
 import argparse
@@ -13,7 +14,7 @@ import nvfp4_sm120_b200 as Q
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["quant", "gemm", "ffn"])
+    ap.add_argument("case", choices=["quant", "gemm", "ffn", "block"])
     ap.add_argument("--rows", type=int, default=16384)
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--mode", default="rne", choices=["rne", "sr", "rht_sr"])
@@ -25,6 +26,7 @@ def main():
     ap.add_argument("--d", type=int, default=4096)
     ap.add_argument("--h", type=int, default=14336)
     ap.add_argument("--micro", type=int, default=8)
+    ap.add_argument("--heads", type=int, default=12, help="block: attention heads (sequence length 1024)")
     ap.add_argument("--bf16", action="store_true", help="ffn: bf16 nn.Linear comparator instead of FP4Linear")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 one-CTA kernel, 2 two-CTA kernel")
@@ -61,6 +63,32 @@ def main():
         fl = a.micro * ffn_flops(a.tokens, a.d, a.h)
         print(f"ffn {'bf16' if a.bf16 else 'fp4'} d={a.d} h={a.h} tokens={a.tokens} x {a.micro}: {ms:.2f} ms/step, "
               f"{fl / ms / 1e9:.0f} TFLOP/s")
+        return
+    if a.case == "block":
+        # one decoder block of the GPT model (attention + squared-ReLU MLP), forward + backward
+        from nvfp4_sm120_b200.models import DecoderBlock, rotary_tables
+        Q.set_amortize(True)
+        torch.manual_seed(0)
+        blk = DecoderBlock(a.d, a.heads, a.heads, 4 * a.d, not a.bf16, dev)
+        seq = 1024
+        x = torch.randn(a.tokens // seq, seq, a.d, device=dev, dtype=torch.float32, generator=g).requires_grad_(True)
+        cos, sin = rotary_tables(seq, a.d // a.heads, dev)
+
+        def step():
+            Q.mark_step()
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                y = blk(x, cos, sin)
+            y.float().square().mean().backward()
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(a.iters):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"block {'bf16' if a.bf16 else 'fp4'} d={a.d} heads={a.heads} tokens={a.tokens}: "
+              f"{e0.elapsed_time(e1) / a.iters:.3f} ms per forward+backward")
         return
     if a.case == "quant":
         x = torch.randn(a.rows, a.cols, device=dev, dtype=torch.bfloat16, generator=g)
