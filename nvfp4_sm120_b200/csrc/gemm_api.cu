@@ -1,0 +1,72 @@
+// nvfp4_gemm: argument checks, tensor maps, kernel choice (C ABI; declared in include/nvfp4_b200.h).
+#include "gemm_common.cuh"
+
+namespace nvfp4 { namespace gemm2 {
+int launch_2cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const gemm::Params& p,
+                cudaStream_t stream);
+}}
+namespace nvfp4 { namespace gemm3 {
+int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const gemm::Params& p,
+                cudaStream_t stream);
+}}
+namespace nvfp4 { namespace gemm {
+int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const Params& p,
+                cudaStream_t stream);
+}}
+
+static int g_gemm_mode = 0;
+extern "C" int nvfp4_gemm_set_mode(int mode) {
+  if (mode < 0 || mode > 3) return NVFP4_E_MODE;
+  g_gemm_mode = mode;
+  return NVFP4_OK;
+}
+
+// Automatic choice: the persistent pair kernel (mode 3), which measured fastest on every shape with
+// more than one row tile; the one-CTA kernel when M <= 128 (a pair would compute 128 rows of padding)
+// and for the split-K case below.  Modes 1-3 force a kernel, for tuning and tests.
+extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
+                          const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
+                          int64_t K, int64_t ldd, int32_t* status, void* stream_) {
+  using namespace nvfp4::gemm;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!a_q || !a_sf || !a_pts || !b_q || !b_sf || !b_pts || !d) return NVFP4_E_NULL;
+  if (M <= 0 || N <= 0 || K <= 0 || (K & 31) != 0 || ldd < N) return NVFP4_E_SHAPE;
+  if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return NVFP4_E_SHAPE;
+  if (out_dtype != NVFP4_OUT_BF16 && out_dtype != NVFP4_OUT_F32) return NVFP4_E_MODE;
+  auto mis = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  if (mis(a_q, 16) || mis(b_q, 16) || mis(a_sf, 16) || mis(b_sf, 16) || mis(d, 16)) return NVFP4_E_ALIGN;
+  // split K (one-CTA kernel only, see below) when a small fp32 output would leave most SMs idle
+  const int64_t tiles_1cta = ((N + 255) / 256) * ((M + 127) / 128), slices = (K + 255) / 256;
+  const bool want_split = out_dtype == NVFP4_OUT_F32 && tiles_1cta <= 74 && slices >= 16;
+  const int mode = g_gemm_mode != 0 ? g_gemm_mode : ((M > 128 && !want_split) ? 3 : 1);
+  const bool pair = mode >= 2;
+  CUtensorMap map_a, map_b;
+  if (!make_operand_map(&map_a, a_q, M, K, 128) || !make_operand_map(&map_b, b_q, N, K, pair ? 128 : 256))
+    return NVFP4_E_DRIVER;
+  Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status, 1, 0};
+  // Split K when a small fp32 output (the weight gradient: few tiles, K = tokens) would leave most SMs
+  // idle: the CTAs of a tile add their partial sums into the zeroed output.  Summation order then
+  // varies from run to run in the last bits, so it is used only where it pays: fewer tiles than half
+  // the SMs and at least 16 K slices (8 or more per CTA).
+  if (!pair && want_split) {
+    {
+      int64_t s = 148 / tiles_1cta;
+      if (s > slices / 8) s = slices / 8;              // at least 8 slices per CTA
+      if (s > 1) {
+        p.splits = (int)s;
+        cudaError_t e = (ldd == N) ? cudaMemsetAsync(d, 0, (size_t)M * N * 4, stream)
+                                   : cudaMemset2DAsync(d, (size_t)ldd * 4, 0, (size_t)N * 4, (size_t)M, stream);
+        if (e != cudaSuccess) return NVFP4_E_LAUNCH;
+      }
+    }
+  }
+  // The epilogue stores through TMA when the row pitch allows a tensor map (a multiple of 16 bytes)
+  // and the output is written, not accumulated into.
+  CUtensorMap map_d = map_a;                                   // placeholder when unused
+  if (p.splits == 1 && (ldd * (p.out_f32 ? 4 : 2)) % 16 == 0) {
+    if (!make_output_map(&map_d, d, M, N, ldd, p.out_f32 != 0)) return NVFP4_E_DRIVER;
+    p.tma_store = 1;
+  }
+  if (mode == 3) return nvfp4::gemm3::launch_pair(map_a, map_b, map_d, p, stream);
+  return pair ? nvfp4::gemm2::launch_2cta(map_a, map_b, map_d, p, stream) : launch_1cta(map_a, map_b, map_d, p, stream);
+}
