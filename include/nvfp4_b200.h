@@ -93,9 +93,10 @@ int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
  * that HBM is read once.  Bit-identical outputs.  `workspace` is caller scratch of at least
  * nvfp4_quantize_fused_workspace_bytes() bytes (16-byte aligned) that must be ALL ZERO before
  * its first use (one cudaMemset after allocating it); every call that ends normally leaves it
- * all zero again, so it can be reused by the next call without clearing.  int32 word 2 of the
+ * ready for the next call (it carries a launch counter and two alternating barrier slots, each
+ * launch clearing the slot of the next), so it is reused without clearing.  int32 word 4 of the
  * workspace becomes non-zero when a bounded wait inside the kernel gave up (outputs are then
- * undefined; clear the workspace before using it again).  Calls that share a workspace must not
+ * undefined; clear the whole workspace before using it again).  Calls that share a workspace must not
  * overlap on the GPU: use one workspace per stream.  Needs rows * cols / 16 < 2^31.
  * Replaces the whole body of quant_nvfp4_cuda (nvfp4_cuda.py:158-187): amax, pts, quant_launch,
  * to_blocked.

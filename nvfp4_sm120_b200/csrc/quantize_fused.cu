@@ -31,15 +31,18 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 constexpr int kBatch = 4;                          // blocks per thread in flight, amax pass
 constexpr int kBatch2 = 2;                         // same, quantize pass (register budget: 64)
 
-struct Workspace {          // 64 bytes of caller scratch: all zero before the first call; every
-  float amax;               // launch that ends normally leaves it all zero again
-  unsigned int arrived;
-  int error;                // sticky: 1 = the grid barrier gave up, 2 = a bulk copy never landed
-  unsigned int done;
-  unsigned long long stamp[5];   // diagnostics: globaltimer of CTA 0 at start, after the streamed
-                                 // amax, after the stashed amax, after the barrier, at the end
-  unsigned long long last_end;   // latest end over all CTAs of the last launch (diagnostics)
+struct Workspace {          // 64 bytes of caller scratch, all zero before the first call.  Launch number e
+  float amax[2];            // (counted in `epoch`) uses slot e & 1 of the maximum and of the arrival
+  unsigned int arrived[2];  // counter and, once its grid barrier has opened, zeroes the other slot for
+  int error;                // launch e + 1 and bumps `epoch`: nothing is left to do at the end of the
+  unsigned int epoch;       // kernel.  error is sticky: 1 = the grid barrier gave up, 2 = a bulk copy
+                            // never landed.
+  unsigned long long start;      // diagnostics: globaltimer of CTA 0 at its start, then nanoseconds from
+  unsigned int after[4];         // there to: streamed amax done, stashed amax done, barrier open, CTA 0 end
+  unsigned long long last_end;   // latest end over all CTAs of the last launch
+  unsigned int pad[2];
 };
+static_assert(sizeof(Workspace) == 64, "the ABI promises a 64-byte workspace");
 
 struct FastDiv {            // n / d for 0 <= n < 2^31 and a fixed d, as one mulhi and a shift
   uint32_t mul, shift, d;
@@ -196,7 +199,12 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   }
   if (RHT && tid < 16) sgs[tid] = __ldg(signs16 + tid);
   const bool stamper = blockIdx.x == 0 && tid == 0;
-  if (stamper) { ws->stamp[0] = global_ns(); ws->last_end = 0ull; }
+  unsigned long long t_start = 0;
+  if (stamper) { t_start = global_ns(); ws->start = t_start; ws->last_end = 0ull; }
+  // which of the two barrier slots this launch uses (needed only at the barrier: the load has all of
+  // phase 1 to come back)
+  unsigned int epoch = 0;
+  if (tid == 0) asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(&ws->epoch) : "memory");
   __syncthreads();
   uint32_t sm[8];                 // sign-bit masks of the packed bf16 pairs (bit 15: even, bit 31: odd)
 #pragma unroll
@@ -241,7 +249,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) m = fmaxf(m, block_max(min(i + u * kThreads, s0 - 1), w[u]));
   }
-  if (stamper) ws->stamp[1] = global_ns();
+  if (stamper) ws->after[0] = (unsigned int)(global_ns() - t_start);
   if (stash_blocks > 0) {
     bool landed = mbar_try_wait(bar, 0);
     if (!landed) {
@@ -264,7 +272,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
   if ((tid & 31) == 0) red[tid >> 5] = m;
   __syncthreads();
-  if (stamper) ws->stamp[2] = global_ns();
+  if (stamper) ws->after[1] = (unsigned int)(global_ns() - t_start);
 
   // ------------------------------- grid barrier -------------------------------
   if (tid < 32) {
@@ -275,28 +283,39 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 2));
     mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 1));
     if (tid == 0) {
-      atomicMax(reinterpret_cast<unsigned int*>(&ws->amax), __float_as_uint(mm));
-      __threadfence();
-      atomicAdd(&ws->arrived, 1u);
+      const unsigned int slot = epoch & 1u;
+      unsigned int* amax_word = reinterpret_cast<unsigned int*>(&ws->amax[slot]);
+      // non-negative floats order like their bit patterns; the release on the arrival publishes the
+      // maximum before it
+      asm volatile("red.relaxed.gpu.global.max.u32 [%0], %1;" ::"l"(amax_word), "r"(__float_as_uint(mm)) : "memory");
+      asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(&ws->arrived[slot]), "r"(1u) : "memory");
       const unsigned long long t0 = global_ns();
       unsigned int seen;
       uint32_t spins = 0;
       do {
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&ws->arrived) : "memory");
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&ws->arrived[slot]) : "memory");
         if (seen >= gridDim.x) break;
         if ((++spins & 63u) == 0u && global_ns() - t0 > kWaitLimitNs) { *cta_abort = 1; ws->error = 1; break; }
       } while (true);
+      unsigned int amax_bits;
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(amax_bits) : "l"(amax_word) : "memory");
+      red[0] = __uint_as_float(amax_bits);                       // to the whole CTA through shared memory
+      if (blockIdx.x == 0 && *cta_abort == 0) {
+        // every CTA has read `epoch` (it did so before it arrived): prepare the next launch
+        ws->amax[slot ^ 1u] = 0.0f;
+        ws->arrived[slot ^ 1u] = 0u;
+        ws->epoch = epoch + 1u;
+      }
     }
   }
   __syncthreads();
   if (*cta_abort != 0) return;
-  if (stamper) ws->stamp[3] = global_ns();
+  if (stamper) ws->after[2] = (unsigned int)(global_ns() - t_start);
 
   // ------------------------------- phase 2: quantize -------------------------------
   Scale sc;
   {
-    float amax;
-    asm volatile("ld.relaxed.gpu.global.f32 %0, [%1];" : "=f"(amax) : "l"(&ws->amax) : "memory");
+    const float amax = red[0];
     sc.pts = __fdiv_rn(fmaxf(amax, kAmaxFloor), kGlobalDiv);
     sc.inv_pts = __fdiv_rn(1.0f, sc.pts);
     sc.c = __fdiv_rn(1.0f, kF4Max * sc.pts);
@@ -357,18 +376,10 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     for (int u = 0; u < kBatch2; ++u)
       if (i + u * kThreads < s0) quantize(i + u * kThreads, w[u]);
   }
-  // the last CTA to finish puts the workspace back to zero for the next launch
-  __syncthreads();
-  if (stamper) ws->stamp[4] = global_ns();
-  if (tid == 0) {
-    atomicMax(&ws->last_end, global_ns());
-    __threadfence();
-    if (atomicAdd(&ws->done, 1u) == gridDim.x - 1) {
-      ws->amax = 0.0f;
-      ws->arrived = 0u;
-      ws->done = 0u;
-      __threadfence();
-    }
+  if (tid == 0) {                                                // diagnostics only, nothing waits for them
+    const unsigned long long t_end = global_ns();
+    if (stamper) ws->after[3] = (unsigned int)(t_end - t_start);
+    atomicMax(&ws->last_end, t_end);
   }
 }
 

@@ -107,10 +107,12 @@ def main():
               f"{nbytes / ms / 1e6:.0f} GB/s algorithmic")
         if not a.transpose:
             from nvfp4_sm120_b200 import quant
-            st = quant._workspace(dev).view(torch.int64)[2:8].tolist()
+            ws = quant._workspace(dev).cpu()         # start (u64 at byte 24), four u32 offsets, last end (u64)
+            start, last_end = int(ws.view(torch.int64)[3]), int(ws.view(torch.int64)[6])
+            t = [0] + [int(v) & 0xffffffff for v in ws[8:12].tolist()]
             print("CTA 0 phases (us): streamed amax %.1f, stashed amax %.1f, barrier %.1f, quantize %.1f; "
                   "first CTA start to last CTA end %.1f" %
-                  (tuple((st[i + 1] - st[i]) / 1e3 for i in range(4)) + ((st[5] - st[0]) / 1e3,)))
+                  (tuple((t[i + 1] - t[i]) / 1e3 for i in range(4)) + ((last_end - start) / 1e3,)))
     else:
         A = torch.randn(a.m, a.k, device=dev, dtype=torch.bfloat16, generator=g)
         Bt = torch.randn(a.n, a.k, device=dev, dtype=torch.bfloat16, generator=g)

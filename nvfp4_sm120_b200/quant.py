@@ -52,8 +52,8 @@ _WS = {}
 
 
 def _workspace(device):
-    """Zeroed 64-byte scratch of the single-launch quantizer, one per (device, stream): the kernel
-    leaves it zeroed, and launches on one stream never overlap."""
+    """64-byte scratch of the single-launch quantizer, zeroed once, one per (device, stream): every
+    launch leaves it ready for the next, and launches on one stream never overlap."""
     key = (device, torch.cuda.current_stream().cuda_stream)
     if key not in _WS:
         _WS[key] = torch.zeros(16, dtype=torch.int32, device=device)
@@ -65,7 +65,7 @@ def fused_error(device=None) -> int:
     (0 = none).  Reading it synchronises."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     key = (device, torch.cuda.current_stream().cuda_stream)
-    return int(_WS[key][2].item()) if key in _WS else 0
+    return int(_WS[key][4].item()) if key in _WS else 0
 
 
 def _stream():
