@@ -274,6 +274,15 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   __syncthreads();
   if (stamper) ws->after[1] = (unsigned int)(global_ns() - t_start);
 
+  // The first blocks of the quantize pass do not depend on the maximum: their loads (L2 hits by now)
+  // go out before the barrier and are in registers when it opens.
+  uint32_t pre[kBatch2][8];
+  const uint32_t i_first = b0 + tid;
+  if (i_first < s0) {
+#pragma unroll
+    for (int u = 0; u < kBatch2; ++u) load_global(min(i_first + u * kThreads, s0 - 1), pre[u]);
+  }
+
   // ------------------------------- grid barrier -------------------------------
   if (tid < 32) {
     float mm = red[tid];
@@ -359,13 +368,13 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     const uint32_t tile = (r >> 7) * col_tiles + (kb >> 2);
     scales[(size_t)tile * 512 + ((r & 31u) << 4) + (((r >> 5) & 3u) << 2) + (kb & 3u)] = (uint8_t)sf;
   };
-  // stashed tail first (no global read), then the streamed head out of the L2
-  for (uint32_t i = s0 + tid; i < b1; i += kThreads) {
-    uint32_t w[8];
-    load_stash(i, w);
-    quantize(i, w);
+  // the streamed head out of the L2 (first batch already loaded), then the stashed tail
+  if (i_first < s0) {
+#pragma unroll
+    for (int u = 0; u < kBatch2; ++u)
+      if (i_first + u * kThreads < s0) quantize(i_first + u * kThreads, pre[u]);
   }
-  for (uint32_t i = b0 + tid; i < s0; i += kBatch2 * kThreads) {
+  for (uint32_t i = i_first + kBatch2 * kThreads; i < s0; i += kBatch2 * kThreads) {
     uint32_t w[kBatch2][8];
 #pragma unroll
     for (int u = 0; u < kBatch2; ++u) {
@@ -375,6 +384,11 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
 #pragma unroll
     for (int u = 0; u < kBatch2; ++u)
       if (i + u * kThreads < s0) quantize(i + u * kThreads, w[u]);
+  }
+  for (uint32_t i = s0 + tid; i < b1; i += kThreads) {
+    uint32_t w[8];
+    load_stash(i, w);
+    quantize(i, w);
   }
   if (tid == 0) {                                                // diagnostics only, nothing waits for them
     const unsigned long long t_end = global_ns();

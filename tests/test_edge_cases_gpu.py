@@ -65,6 +65,15 @@ def test_many_calls_reuse_workspace_without_leaking_state(Q):
     for rep in range(3):
         for x in xs:
             assert _same(Q.quant_nvfp4(x.cuda()), O.quant_nvfp4(x))
+    # a large maximum followed by small ones, on grids of different sizes: a barrier slot that was not
+    # cleared would carry the old maximum (or an old arrival count) into the next launch
+    g = torch.Generator().manual_seed(77)
+    big = (torch.randn(2048, 1024, generator=g) * 1000).to(torch.bfloat16)
+    small = (torch.randn(48, 64, generator=g) * 1e-3).to(torch.bfloat16)
+    mid = torch.randn(700, 512, generator=g).to(torch.bfloat16)
+    want = {id(t): O.quant_nvfp4(t) for t in (big, small, mid)}
+    for t in (big, small, small, mid, big, small, mid, mid, small):
+        assert _same(Q.quant_nvfp4(t.cuda()), want[id(t)])
     assert quant.fused_error() == 0
 
 
