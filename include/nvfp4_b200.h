@@ -150,6 +150,30 @@ int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
  */
 int nvfp4_gemm_set_mode(int mode);
 
+/*
+ * Producer fusion in front of the quantizer: SwiGLU and its backward in one pass each that also
+ * leaves the per-tensor maxima the following quantizations need, so that those run as one
+ * nvfp4_quantize_bf16 call with the amax given (no separate amax pass).
+ *   fwd: out = silu(gate) * up; maxima2[0] = max|out|, maxima2[1] = max|RHT(out)| where RHT is the
+ *        16-point random-sign Hadamard along the ROW dimension in groups of 16 rows (the transform of
+ *        the transposing quantizer, nvfp4_quantize_bf16 with transpose = 1, rht = 1).
+ *   bwd: dgate = dout * up * silu'(gate), dup = dout * silu(gate); maxima4 = {max|dgate|,
+ *        max|RHT(dgate)|, max|dup|, max|RHT(dup)|}.
+ * All tensors [rows, cols] bf16 row-major (cols even; inputs with leading dimension ld_in, outputs
+ * ld_out).  fp32 arithmetic, one rounding to bf16; the maxima are taken over the rounded values with
+ * the operations of nvfp4_amax_bf16, so they equal what nvfp4_amax_bf16 would return for the stored
+ * tensors.  signs16 == NULL skips the RHT maxima (then rows need not be a multiple of 16).
+ * zero_first != 0 clears the maxima first; with 0 the call max-accumulates into them.
+ * The reference computes these with torch element-wise kernels; it has no fused counterpart
+ * (its models use a squared-ReLU MLP, nvfp4_train.py:120-123; SwiGLU is its FFN benchmark block).
+ */
+int nvfp4_swiglu_fwd_bf16(const void* gate, const void* up, int64_t rows, int64_t cols, int64_t ld_in,
+                          void* out, int64_t ld_out, const float* signs16, float* maxima2,
+                          int zero_first, void* stream);
+int nvfp4_swiglu_bwd_bf16(const void* gate, const void* up, const void* dout, int64_t rows, int64_t cols,
+                          int64_t ld_in, void* dgate, void* dup, int64_t ld_out, const float* signs16,
+                          float* maxima4, int zero_first, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,14 +8,18 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .linear import make_linear
+from .linear import FP4Linear, make_linear
+from .swiglu import swiglu
 
 
 class SwiGLUFFN(nn.Module):
-    """y = down(silu(gate(x)) * up(x)); every linear is an FP4Linear when use_fp4."""
+    """y = down(silu(gate(x)) * up(x)); every linear is an FP4Linear when use_fp4.  With FP4 linears
+    and bf16 activations the SwiGLU product and its backward run as fused kernels that also hand
+    the following quantizations their per-tensor maxima (fused=False keeps the torch ops)."""
 
-    def __init__(self, d_model, hidden, use_fp4=True, device="cuda", seed=None):
+    def __init__(self, d_model, hidden, use_fp4=True, device="cuda", seed=None, fused=True):
         super().__init__()
+        self.fused = bool(fused and use_fp4)
         self.gate = make_linear(d_model, hidden, use_fp4, device)
         self.up = make_linear(d_model, hidden, use_fp4, device)
         self.down = make_linear(hidden, d_model, use_fp4, device)
@@ -27,8 +31,17 @@ class SwiGLUFFN(nn.Module):
                 bound = 1.0 / math.sqrt(lin.weight.shape[1])          # kaiming_uniform_(a=sqrt(5))
                 lin.weight.uniform_(-bound, bound, generator=g)
 
+        # one sign vector serves the maxima of both gradient tensors in the fused backward
+        if self.fused and not (torch.equal(self.gate.signs, self.up.signs) and
+                               torch.equal(self.gate.signs, self.down.signs)):
+            self.fused = False
+
     def forward(self, x):
-        return self.down(F.silu(self.gate(x)) * self.up(x))
+        g, u = self.gate(x), self.up(x)
+        if self.fused and isinstance(self.down, FP4Linear) and g.dtype == torch.bfloat16 and g.is_cuda:
+            h, h_max = swiglu(g, u, self.gate.signs if g.numel() // g.shape[-1] % 16 == 0 else None)
+            return self.down(h, amax=h_max)
+        return self.down(F.silu(g) * u)
 
 
 def ffn_flops(tokens, d_model, hidden):

@@ -32,6 +32,26 @@ _AMORTIZE = os.environ.get("NVFP4_AMORTIZE", "0") == "1"
 def mark_step():
     """Invalidate every FP4Linear's cached weight quantization (call after optimizer.step())."""
     _STEP[0] += 1
+    _GRAD_AMAX.clear()
+
+
+# Maxima of gradient tensors that a fused producer already knows (swiglu.SwiGLUFn.backward): keyed by
+# the address of the gradient, which the entry keeps alive so that the address cannot be reused while
+# the hint exists.  FP4LinearFn.backward takes the hint of the gradient it is handed and then skips
+# its amax passes.  Entries that are never taken are dropped by mark_step().
+_GRAD_AMAX = {}
+
+
+def hint_grad_amax(grad, maxima2, has_rht):
+    """maxima2: fp32 [2] on the device = max|grad| and max|RHT_tokens(grad)| (valid if has_rht)."""
+    _GRAD_AMAX[grad.data_ptr()] = (grad, maxima2, bool(has_rht))
+
+
+def _take_grad_amax(gy2):
+    e = _GRAD_AMAX.pop(gy2.data_ptr(), None)
+    if e is None or e[0].numel() != gy2.numel() or e[0].dtype != gy2.dtype or e[0].shape[-1] != gy2.shape[-1]:
+        return None, None
+    return e[1][0:1], (e[1][1:2] if e[2] else None)
 
 
 def set_amortize(flag: bool):
@@ -50,17 +70,21 @@ class FP4LinearFn(torch.autograd.Function):
     word of a tensor that is sharded across ranks before it is used (tensor parallelism)."""
 
     @staticmethod
-    def forward(ctx, x, w, H, signs, wq_K, wq_N, amax_reduce=None, sharded=(False, False)):
+    def forward(ctx, x, w, H, signs, wq_K, wq_N, amax_reduce=None, sharded=(False, False), x_amax=None):   # callers pass all nine
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         x_sharded, y_sharded = sharded                 # is the K dim / the N dim split across ranks?
-        xq = _quant(x2, amax_reduce if x_sharded else None)
+        # x_amax: fp32 [2] from a fused producer = max|x| and max|RHT_tokens(x)| (what the two amax
+        # passes over x would find); the token count must then be a multiple of 16
+        if x_amax is not None and (x2.shape[0] % BLK != 0 or x2.dtype != torch.bfloat16):
+            x_amax = None
+        xq = _quant(x2, amax_reduce if x_sharded else None, amax=None if x_amax is None else x_amax[0:1])
         if wq_K is None:
             wq_K = _quant(w, amax_reduce)
         y = nvfp4_mm(xq, wq_K.t(), torch.bfloat16)
         ctx.save_for_backward(x2, w)
         ctx.H, ctx.signs, ctx.xshape, ctx.wq_N = H, signs, x.shape, wq_N
-        ctx.amax_reduce, ctx.sharded = amax_reduce, sharded
+        ctx.amax_reduce, ctx.sharded, ctx.x_amax = amax_reduce, sharded, x_amax
         return y.reshape(*x.shape[:-1], w.shape[0]).to(x.dtype)
 
     @staticmethod
@@ -69,26 +93,30 @@ class FP4LinearFn(torch.autograd.Function):
         H, signs, wq_N, red = ctx.H, ctx.signs, ctx.wq_N, ctx.amax_reduce
         x_sharded, y_sharded = ctx.sharded
         gy2 = gy.reshape(-1, w.shape[0])
+        g_amax, g_amax_rht = _take_grad_amax(gy2)      # known to a fused producer of gy, else None
+        x_amax_rht = None if ctx.x_amax is None else ctx.x_amax[1:2]
         dx = dw = None
         if ctx.needs_input_grad[0]:
             # dgrad: dX = dY @ W, contraction over N; dY gets stochastic rounding
-            gq = _quant(gy2, red if y_sharded else None, stochastic=True)
+            gq = _quant(gy2, red if y_sharded else None, stochastic=True, amax=g_amax)
             if wq_N is None:
                 wq_N = _quant(w, red, transpose=True)
             dx = nvfp4_mm(gq, wq_N.t(), torch.bfloat16).reshape(ctx.xshape).to(gy.dtype)
         if ctx.needs_input_grad[1]:
             # wgrad: dW = dY^T @ X, contraction over tokens; Hadamard on both, SR on the gradient
             gtq = _quant(gy2, red if y_sharded else None, stochastic=True, rht=True, H=H, signs=signs,
-                         transpose=True)
-            xtq = _quant(x2, red if x_sharded else None, rht=True, H=H, signs=signs, transpose=True)
+                         transpose=True, amax=g_amax_rht)
+            xtq = _quant(x2, red if x_sharded else None, rht=True, H=H, signs=signs, transpose=True,
+                         amax=x_amax_rht)
             dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
-        return dx, dw, None, None, None, None, None, None
+        return dx, dw, None, None, None, None, None, None, None
 
 
-def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False):
+def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False, amax=None):
+    """amax: the per-tensor maximum if a producer already knows it (this rank's part when sharded)."""
     if amax_reduce is None:
-        return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose)
-    amax = tensor_amax(t, rht, signs, transpose)
+        return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose, amax=amax)
+    amax = tensor_amax(t, rht, signs, transpose) if amax is None else amax.clone()
     amax_reduce(amax)
     return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose, amax=amax)
 
@@ -142,11 +170,12 @@ class FP4Linear(nn.Module):
     def _wq_N(self):
         return self._cache.wq_N
 
-    def forward(self, x):
+    def forward(self, x, amax=None):
+        """amax: optional fp32 [2] from a fused producer of x (see FP4LinearFn.forward)."""
         if x.is_cuda and torch.is_autocast_enabled("cuda"):
             x = x.to(torch.get_autocast_dtype("cuda"))       # what autocast does for nn.Linear
         wq_K, wq_N = self._cache.get(self.weight)
-        return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N)
+        return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, None, (False, False), amax)
 
     def extra_repr(self):
         return f"in_features={self.weight.shape[1]}, out_features={self.weight.shape[0]}, bias=False, nvfp4"

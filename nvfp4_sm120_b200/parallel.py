@@ -78,7 +78,7 @@ def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
 
 def _fp4_linear_fn(x, w, H, signs, wq_K, wq_N, amax_reduce, sharded):
     from .linear import FP4LinearFn
-    return FP4LinearFn.apply(x, w, H, signs, wq_K, wq_N, amax_reduce, sharded)
+    return FP4LinearFn.apply(x, w, H, signs, wq_K, wq_N, amax_reduce, sharded, None)
 
 
 # ------------------------------------------------------------------------------------------

@@ -1,0 +1,67 @@
+"""Fused SwiGLU in front of the quantizer: h = silu(g) * u (and its backward) in one pass each that also
+leaves the per-tensor maxima the next NVFP4 quantizations need (plain, and after the 16-point Hadamard
+along the token dimension), so FP4Linear can skip its amax passes: the down projection gets the maxima
+of h explicitly, the gate / up projections find the maxima of their output gradients through
+`linear.hint_grad_amax`.  The reference does this with torch element-wise kernels and separate amax
+reductions inside its quantizer (nvfp4_cuda.py:158-165)."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from . import linear as _linear
+from .quant import _signs, _stream
+
+
+def _rows(t):
+    return t.reshape(-1, t.shape[-1])
+
+
+class SwiGLUFn(torch.autograd.Function):
+    """(g, u) -> (h, maxima) with maxima = fp32 [2]: max|h| and max|RHT_tokens(h)| (the second only
+    when `signs` is given and the token count is a multiple of 16, else 0)."""
+
+    @staticmethod
+    def forward(ctx, g, u, signs):
+        if g.dtype != torch.bfloat16 or u.dtype != torch.bfloat16 or g.shape != u.shape:
+            raise ValueError("fused SwiGLU takes two bf16 tensors of one shape")
+        g2, u2 = _rows(g).contiguous(), _rows(u).contiguous()
+        rows, cols = g2.shape
+        use_rht = signs is not None and rows % 16 == 0
+        sg = _signs(signs, g.device) if use_rht else None
+        h = torch.empty_like(g2)
+        maxima = torch.empty(2, dtype=torch.float32, device=g.device)
+        code = _lib.lib().nvfp4_swiglu_fwd_bf16(g2.data_ptr(), u2.data_ptr(), rows, cols, g2.stride(0), h.data_ptr(),
+                                                h.stride(0), sg.data_ptr() if use_rht else None, maxima.data_ptr(),
+                                                1, _stream())
+        _lib.check(code, "nvfp4_swiglu_fwd_bf16")
+        ctx.save_for_backward(g2, u2)
+        ctx.sg, ctx.use_rht, ctx.shape = sg, use_rht, g.shape
+        ctx.mark_non_differentiable(maxima)
+        return h.reshape(g.shape), maxima
+
+    @staticmethod
+    def backward(ctx, dh, _dmax):
+        g2, u2 = ctx.saved_tensors
+        d2 = _rows(dh)
+        if d2.dtype != torch.bfloat16:
+            d2 = d2.to(torch.bfloat16)
+        d2 = d2.contiguous()
+        rows, cols = g2.shape
+        dg, du = torch.empty_like(g2), torch.empty_like(g2)
+        maxima = torch.empty(4, dtype=torch.float32, device=g2.device)
+        code = _lib.lib().nvfp4_swiglu_bwd_bf16(g2.data_ptr(), u2.data_ptr(), d2.data_ptr(), rows, cols, g2.stride(0),
+                                                dg.data_ptr(), du.data_ptr(), dg.stride(0),
+                                                ctx.sg.data_ptr() if ctx.use_rht else None, maxima.data_ptr(), 1,
+                                                _stream())
+        _lib.check(code, "nvfp4_swiglu_bwd_bf16")
+        dg, du = dg.reshape(ctx.shape), du.reshape(ctx.shape)
+        # the linears that produced g and u will quantize exactly these tensors in their backward
+        _linear.hint_grad_amax(dg, maxima[0:2], ctx.use_rht)
+        _linear.hint_grad_amax(du, maxima[2:4], ctx.use_rht)
+        return dg, du, None
+
+
+def swiglu(g, u, signs=None):
+    """h = silu(g) * u and the maxima of h (see SwiGLUFn)."""
+    return SwiGLUFn.apply(g, u, signs)

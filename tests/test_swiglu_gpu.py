@@ -1,0 +1,107 @@
+"""Fused SwiGLU (+ backward) with the maxima for the following quantizers: values against an fp32
+torch reference, maxima bit-equal to the stand-alone amax kernels, and the FFN built on it against
+the FFN built from torch element-wise ops."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def Q():
+    import nvfp4_sm120_b200 as pkg
+    return pkg
+
+
+def _bits(t):
+    return t.view(torch.int32)
+
+
+@pytest.mark.parametrize("shape", [(16, 32), (256, 384), (1024, 14336), (48, 144)])
+def test_forward_values_and_maxima(Q, shape):
+    from nvfp4_sm120_b200 import quant
+    from nvfp4_sm120_b200.swiglu import swiglu
+    from oracle import nvfp4_oracle as O
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    g = (torch.randn(*shape, device="cuda", generator=gen) * 2).to(torch.bfloat16)
+    u = torch.randn(*shape, device="cuda", generator=gen).to(torch.bfloat16)
+    signs = O.signs_from_seed(3).cuda()
+    h, mx = swiglu(g, u, signs)
+    ref = F.silu(g.float()) * u.float()
+    assert h.dtype == torch.bfloat16 and h.shape == g.shape
+    # one rounding to bf16 of an fp32 result computed with fast exp / divide
+    assert torch.allclose(h.float(), ref, rtol=2.0 ** -7, atol=1e-6)
+    # the maxima are those of the stored tensor, bit for bit
+    assert torch.equal(_bits(mx[0:1]), _bits(quant.tensor_amax(h)))
+    assert torch.equal(_bits(mx[1:2]), _bits(quant.tensor_amax(h, rht=True, signs=signs, transpose=True)))
+    # so a quantizer that is handed them produces the bytes of the stand-alone path
+    a = Q.quant_nvfp4(h, amax=mx[0:1])
+    b = Q.quant_nvfp4(h)
+    assert torch.equal(a.qdata, b.qdata) and torch.equal(a.scale.view(torch.uint8), b.scale.view(torch.uint8))
+    at = Q.quant_nvfp4(h, rht=True, signs=signs, transpose=True, amax=mx[1:2])
+    bt = Q.quant_nvfp4(h, rht=True, signs=signs, transpose=True)
+    assert torch.equal(at.qdata, bt.qdata) and torch.equal(at.scale.view(torch.uint8), bt.scale.view(torch.uint8))
+
+
+def test_rows_not_multiple_of_16_skip_the_row_transform(Q):
+    from nvfp4_sm120_b200 import quant
+    from nvfp4_sm120_b200.swiglu import swiglu
+    g = torch.randn(37, 64, device="cuda").to(torch.bfloat16)
+    u = torch.randn(37, 64, device="cuda").to(torch.bfloat16)
+    h, mx = swiglu(g, u, torch.ones(16, device="cuda"))
+    assert torch.allclose(h.float(), F.silu(g.float()) * u.float(), rtol=2.0 ** -7, atol=1e-6)
+    assert torch.equal(_bits(mx[0:1]), _bits(quant.tensor_amax(h))) and float(mx[1]) == 0.0
+
+
+def test_backward_values_maxima_and_hints(Q):
+    from nvfp4_sm120_b200 import linear, quant
+    from nvfp4_sm120_b200.swiglu import swiglu
+    from oracle import nvfp4_oracle as O
+    gen = torch.Generator(device="cuda").manual_seed(6)
+    g = (torch.randn(512, 768, device="cuda", generator=gen) * 2).to(torch.bfloat16).requires_grad_(True)
+    u = torch.randn(512, 768, device="cuda", generator=gen).to(torch.bfloat16).requires_grad_(True)
+    dh = torch.randn(512, 768, device="cuda", generator=gen).to(torch.bfloat16)
+    signs = O.signs_from_seed(3).cuda()
+    linear._GRAD_AMAX.clear()
+    h, _ = swiglu(g, u, signs)
+    dg, du = torch.autograd.grad(h, [g, u], grad_outputs=dh)
+    gf, uf = g.detach().float().requires_grad_(True), u.detach().float().requires_grad_(True)
+    rg, ru = torch.autograd.grad(F.silu(gf) * uf, [gf, uf], grad_outputs=dh.float())
+    assert torch.allclose(dg.float(), rg, rtol=2.0 ** -6, atol=1e-5)
+    assert torch.allclose(du.float(), ru, rtol=2.0 ** -6, atol=1e-5)
+    # the hints registered for the two gradients are the maxima of the stored gradients
+    for t in (dg, du):
+        plain, rht = linear._take_grad_amax(t.reshape(-1, t.shape[-1]))
+        assert torch.equal(_bits(plain), _bits(quant.tensor_amax(t)))
+        assert torch.equal(_bits(rht), _bits(quant.tensor_amax(t, rht=True, signs=signs, transpose=True)))
+    assert linear._take_grad_amax(dg)[0] is None            # taken once
+
+
+def test_fused_ffn_matches_unfused_ffn(Q):
+    """Same weights, same input, same stochastic-rounding seeds: the fused block differs from the torch
+    element-wise block only through the single rounding of h and of the two gradients."""
+    from nvfp4_sm120_b200 import quant
+    from nvfp4_sm120_b200.ffn import SwiGLUFFN
+    Q.set_amortize(False)
+    a = SwiGLUFFN(256, 512, use_fp4=True, device="cuda", seed=4, fused=True)
+    b = SwiGLUFFN(256, 512, use_fp4=True, device="cuda", seed=4, fused=False)
+    assert a.fused and not b.fused
+    x = torch.randn(128, 256, device="cuda").to(torch.bfloat16)
+    gy = torch.randn(128, 256, device="cuda").to(torch.bfloat16)
+    outs = []
+    for m in (a, b):
+        quant._SEED[0] = 1000
+        xi = x.clone().requires_grad_(True)
+        y = m(xi)
+        grads = torch.autograd.grad(y, [xi] + list(m.parameters()), grad_outputs=gy)
+        outs.append((y, grads))
+    (ya, ga), (yb, gb) = outs
+    rel = lambda p, q: ((p.float() - q.float()).norm() / q.float().norm()).item()
+    assert rel(ya, yb) < 5e-2                    # bf16-ulp changes of h flip some FP4 codes
+    for p, q in zip(ga, gb):
+        assert rel(p, q) < 0.15                  # FP4 noise of a changed operand, not an error in the recipe
+    # against exact arithmetic both are equally far
+    wg, wu, wd = [p.detach().float() for p in a.parameters()]
+    exact = (F.silu(x.float() @ wg.t()) * (x.float() @ wu.t())) @ wd.t()
+    assert abs(rel(ya, exact) - rel(yb, exact)) < 2e-2 and rel(ya, exact) < 0.3
