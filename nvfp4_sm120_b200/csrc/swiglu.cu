@@ -191,6 +191,158 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint16_t* __restr
   cta_max_to_global<4>(m, maxima, use);
 }
 
+// ---- wide variants: row-contiguous 16-byte accesses, the 16-row column view through shared memory ----
+// A CTA works on tiles of 16 rows x 512 columns.  Element-wise phase: thread t and step k own the
+// eight columns 8 * (t % 64) of row 4 * k + t / 64, so a warp moves 512 contiguous bytes of a row per
+// instruction; the rounded results also go to a shared tile.  Column phase: thread t reads its two
+// columns of all 16 rows from the tile (consecutive lanes, consecutive banks) for the Hadamard maxima.
+// The narrow kernels above stay for shapes without 16-byte rows.
+constexpr int kTileCols = 512;
+constexpr int kPitchWords = kTileCols / 2 + 4;            // 32-bit words per tile row, padded
+
+__device__ __forceinline__ uint4 ldg16(const uint16_t* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+__device__ __forceinline__ void tile_rht_max(const uint32_t* tile, const float (&sg)[16], bool active, float& m_rht) {
+  if (!active) return;
+  float v0[16], v1[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t w = tile[i * kPitchWords + threadIdx.x];
+    v0[i] = bf16_lo(w) * sg[i];
+    v1[i] = bf16_hi(w) * sg[i];
+  }
+  hadamard16_inplace(v0);
+  hadamard16_inplace(v1);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m_rht = fmaxf(m_rht, fmaxf(fabsf(v0[i]), fabsf(v1[i])));
+}
+
+__global__ void __launch_bounds__(256) swiglu_fwd_wide_kernel(const uint16_t* __restrict__ gate,
+                                                              const uint16_t* __restrict__ up, int64_t rows,
+                                                              int64_t cols, int64_t ld_in, uint16_t* __restrict__ out,
+                                                              int64_t ld_out, const float* __restrict__ signs16,
+                                                              float* __restrict__ maxima) {
+  __shared__ __align__(16) uint32_t tile[16 * kPitchWords];
+  const bool rht = signs16 != nullptr;
+  float sg[16];
+  if (rht) load_signs(signs16, sg);
+  const int64_t c0 = (int64_t)blockIdx.x * kTileCols;
+  const int cc = (threadIdx.x & 63) * 8;
+  const bool col_in = c0 + cc < cols;                       // cols is a multiple of 8 here
+  float m[2] = {0.0f, 0.0f};
+#pragma unroll 1
+  for (int j = 0; j < kRowBlocks; ++j) {
+    const int64_t r0 = ((int64_t)blockIdx.y * kRowBlocks + j) * 16;
+    if (r0 >= rows) break;                                   // uniform across the CTA
+    uint4 g4[4], u4[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int64_t r = r0 + 4 * k + (threadIdx.x >> 6);
+      const bool in = col_in && r < rows;
+      g4[k] = in ? ldg16(gate + r * ld_in + c0 + cc) : make_uint4(0, 0, 0, 0);
+      u4[k] = in ? ldg16(up + r * ld_in + c0 + cc) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t gw[4] = {g4[k].x, g4[k].y, g4[k].z, g4[k].w}, uw[4] = {u4[k].x, u4[k].y, u4[k].z, u4[k].w};
+      uint32_t hw[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float a0 = bf16_lo(gw[q]), a1 = bf16_hi(gw[q]);
+        hw[q] = pack_bf16x2(a0 * sigmoidf(a0) * bf16_lo(uw[q]), a1 * sigmoidf(a1) * bf16_hi(uw[q]));
+        m[0] = fmaxf(m[0], fmaxf(fabsf(bf16_lo(hw[q])), fabsf(bf16_hi(hw[q]))));
+      }
+      const int rl = 4 * k + (threadIdx.x >> 6);
+      const int64_t r = r0 + rl;
+      const uint4 h4 = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+      if (col_in && r < rows) *reinterpret_cast<uint4*>(out + r * ld_out + c0 + cc) = h4;
+      if (rht) *reinterpret_cast<uint4*>(&tile[rl * kPitchWords + (cc >> 1)]) = h4;
+    }
+    if (rht) {
+      __syncthreads();
+      tile_rht_max(tile, sg, c0 + 2 * (int64_t)threadIdx.x < cols, m[1]);
+      __syncthreads();
+    }
+  }
+  const bool use[2] = {true, rht};
+  cta_max_to_global<2>(m, maxima, use);
+}
+
+__global__ void __launch_bounds__(256) swiglu_bwd_wide_kernel(const uint16_t* __restrict__ gate,
+                                                              const uint16_t* __restrict__ up,
+                                                              const uint16_t* __restrict__ dh, int64_t rows,
+                                                              int64_t cols, int64_t ld_in,
+                                                              uint16_t* __restrict__ dgate, uint16_t* __restrict__ dup,
+                                                              int64_t ld_out, const float* __restrict__ signs16,
+                                                              float* __restrict__ maxima) {
+  __shared__ __align__(16) uint32_t tile_g[16 * kPitchWords];
+  __shared__ __align__(16) uint32_t tile_u[16 * kPitchWords];
+  const bool rht = signs16 != nullptr;
+  float sg[16];
+  if (rht) load_signs(signs16, sg);
+  const int64_t c0 = (int64_t)blockIdx.x * kTileCols;
+  const int cc = (threadIdx.x & 63) * 8;
+  const bool col_in = c0 + cc < cols;
+  float m[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 1
+  for (int j = 0; j < kRowBlocks; ++j) {
+    const int64_t r0 = ((int64_t)blockIdx.y * kRowBlocks + j) * 16;
+    if (r0 >= rows) break;
+#pragma unroll 2
+    for (int k = 0; k < 4; ++k) {
+      const int rl = 4 * k + (threadIdx.x >> 6);
+      const int64_t r = r0 + rl;
+      const bool in = col_in && r < rows;
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      const uint4 g4 = in ? ldg16(gate + r * ld_in + c0 + cc) : z, u4 = in ? ldg16(up + r * ld_in + c0 + cc) : z;
+      const uint4 d4 = in ? ldg16(dh + r * ld_in + c0 + cc) : z;
+      const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
+      uint32_t og[4], ou[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float dgv[2], duv[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float g = h ? bf16_hi(gw[q]) : bf16_lo(gw[q]), u = h ? bf16_hi(uw[q]) : bf16_lo(uw[q]);
+          const float d = h ? bf16_hi(dw[q]) : bf16_lo(dw[q]);
+          const float sgm = sigmoidf(g);
+          duv[h] = d * (g * sgm);
+          dgv[h] = d * u * (sgm * (1.0f + g * (1.0f - sgm)));
+        }
+        og[q] = pack_bf16x2(dgv[0], dgv[1]);
+        ou[q] = pack_bf16x2(duv[0], duv[1]);
+        m[0] = fmaxf(m[0], fmaxf(fabsf(bf16_lo(og[q])), fabsf(bf16_hi(og[q]))));
+        m[2] = fmaxf(m[2], fmaxf(fabsf(bf16_lo(ou[q])), fabsf(bf16_hi(ou[q]))));
+      }
+      const uint4 og4 = make_uint4(og[0], og[1], og[2], og[3]), ou4 = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+      if (in) {
+        *reinterpret_cast<uint4*>(dgate + r * ld_out + c0 + cc) = og4;
+        *reinterpret_cast<uint4*>(dup + r * ld_out + c0 + cc) = ou4;
+      }
+      if (rht) {
+        *reinterpret_cast<uint4*>(&tile_g[rl * kPitchWords + (cc >> 1)]) = og4;
+        *reinterpret_cast<uint4*>(&tile_u[rl * kPitchWords + (cc >> 1)]) = ou4;
+      }
+    }
+    if (rht) {
+      __syncthreads();
+      const bool active = c0 + 2 * (int64_t)threadIdx.x < cols;
+      tile_rht_max(tile_g, sg, active, m[1]);
+      tile_rht_max(tile_u, sg, active, m[3]);
+      __syncthreads();
+    }
+  }
+  const bool use[4] = {true, rht, true, rht};
+  cta_max_to_global<4>(m, maxima, use);
+}
+
+// 16-byte rows everywhere: the wide kernels apply
+static bool wide_ok(const void* a, const void* b, const void* c, const void* o1, const void* o2, int64_t cols,
+                    int64_t ld_in, int64_t ld_out) {
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  return (cols & 7) == 0 && (ld_in & 7) == 0 && (ld_out & 7) == 0 && al(a) && al(b) && al(c) && al(o1) && al(o2);
+}
+
 static int check(const void* a, const void* b, const void* c, const void* o1, const void* o2, int64_t rows,
                  int64_t cols, int64_t ld_in, int64_t ld_out, const float* signs16, const float* maxima) {
   if (!a || !b || !c || !o1 || !o2 || !maxima) return NVFP4_E_NULL;
@@ -217,9 +369,14 @@ extern "C" int nvfp4_swiglu_fwd_bf16(const void* gate, const void* up, int64_t r
   if (rc != NVFP4_OK) return rc;
   if (zero_first && cudaMemsetAsync(maxima2, 0, 2 * sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
   const dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
-  swiglu_fwd_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate), static_cast<const uint16_t*>(up),
-                                               rows, cols, ld_in, static_cast<uint16_t*>(out), ld_out, signs16,
-                                               maxima2);
+  if (wide_ok(gate, up, gate, out, out, cols, ld_in, ld_out))
+    swiglu_fwd_wide_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate),
+                                                      static_cast<const uint16_t*>(up), rows, cols, ld_in,
+                                                      static_cast<uint16_t*>(out), ld_out, signs16, maxima2);
+  else
+    swiglu_fwd_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate), static_cast<const uint16_t*>(up),
+                                                 rows, cols, ld_in, static_cast<uint16_t*>(out), ld_out, signs16,
+                                                 maxima2);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 
@@ -231,9 +388,16 @@ extern "C" int nvfp4_swiglu_bwd_bf16(const void* gate, const void* up, const voi
   if (rc != NVFP4_OK) return rc;
   if (zero_first && cudaMemsetAsync(maxima4, 0, 4 * sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
   const dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
-  swiglu_bwd_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate), static_cast<const uint16_t*>(up),
-                                               static_cast<const uint16_t*>(dh), rows, cols, ld_in,
-                                               static_cast<uint16_t*>(dgate), static_cast<uint16_t*>(dup), ld_out,
-                                               signs16, maxima4);
+  if (wide_ok(gate, up, dh, dgate, dup, cols, ld_in, ld_out))
+    swiglu_bwd_wide_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate),
+                                                      static_cast<const uint16_t*>(up),
+                                                      static_cast<const uint16_t*>(dh), rows, cols, ld_in,
+                                                      static_cast<uint16_t*>(dgate), static_cast<uint16_t*>(dup),
+                                                      ld_out, signs16, maxima4);
+  else
+    swiglu_bwd_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate), static_cast<const uint16_t*>(up),
+                                                 static_cast<const uint16_t*>(dh), rows, cols, ld_in,
+                                                 static_cast<uint16_t*>(dgate), static_cast<uint16_t*>(dup), ld_out,
+                                                 signs16, maxima4);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }

@@ -105,3 +105,32 @@ def test_fused_ffn_matches_unfused_ffn(Q):
     wg, wu, wd = [p.detach().float() for p in a.parameters()]
     exact = (F.silu(x.float() @ wg.t()) * (x.float() @ wu.t())) @ wd.t()
     assert abs(rel(ya, exact) - rel(yb, exact)) < 2e-2 and rel(ya, exact) < 0.3
+
+
+def test_narrow_kernels_match_wide_kernels(Q):
+    """Rows that are not a multiple of 16 bytes take the 4-byte kernels: same values and maxima as the
+    16-byte kernels on a zero-padded copy (silu(0) * 0 = 0 adds nothing to a maximum)."""
+    from nvfp4_sm120_b200 import linear
+    from nvfp4_sm120_b200.swiglu import swiglu
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    rows, cols, pad = 64, 44, 48
+    signs = (torch.randint(0, 2, (16,), device="cuda", generator=gen).float() * 2 - 1)
+    g = torch.zeros(rows, pad, device="cuda", dtype=torch.bfloat16)
+    u = torch.zeros(rows, pad, device="cuda", dtype=torch.bfloat16)
+    d = torch.zeros(rows, pad, device="cuda", dtype=torch.bfloat16)
+    for t in (g, u, d):
+        t[:, :cols] = torch.randn(rows, cols, device="cuda", generator=gen).to(torch.bfloat16)
+    res = []
+    for w in (cols, pad):
+        gi = g[:, :w].contiguous().requires_grad_(True)
+        ui = u[:, :w].contiguous().requires_grad_(True)
+        linear._GRAD_AMAX.clear()
+        h, mx = swiglu(gi, ui, signs)
+        dg, du = torch.autograd.grad(h, [gi, ui], grad_outputs=d[:, :w].contiguous())
+        hints = [linear._GRAD_AMAX[t.data_ptr()][1].clone() for t in (dg, du)]
+        res.append((h[:, :cols], dg[:, :cols], du[:, :cols], mx, hints))
+    linear._GRAD_AMAX.clear()
+    (h0, dg0, du0, mx0, hint0), (h1, dg1, du1, mx1, hint1) = res
+    assert torch.equal(h0, h1) and torch.equal(dg0, dg1) and torch.equal(du0, du1)
+    assert torch.equal(_bits(mx0), _bits(mx1))
+    assert all(torch.equal(_bits(a), _bits(b)) for a, b in zip(hint0, hint1))
