@@ -102,10 +102,14 @@ class _ParallelLinearBase(nn.Module):
             self._cache = None
             self.H = self.signs = None
 
-    def _call(self, x, sharded):
+    def _call(self, x, sharded, x_amax=None):
+        """x_amax: this rank's maxima of x from a fused producer (swiglu.SwiGLUFn), FP4 path only."""
         wq_K = wq_N = None
         if self._cache is not None:
             wq_K, wq_N = self._cache.get(self.weight, self.amax_reduce)
+        if x_amax is not None and self.linear_fn is _fp4_linear_fn:
+            from .linear import FP4LinearFn
+            return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, self.amax_reduce, sharded, x_amax)
         return self.linear_fn(x, self.weight, self.H, self.signs, wq_K, wq_N, self.amax_reduce, sharded)
 
 
@@ -122,8 +126,8 @@ class RowParallelFP4Linear(_ParallelLinearBase):
     """y[*, out] = sum over ranks of x_local @ W_local^T.  The input is split along the feature dim
     (its amax is reduced); the output is summed over the group and is then replicated."""
 
-    def forward(self, x_local):
-        y = self._call(x_local, (True, False))
+    def forward(self, x_local, amax=None):
+        y = self._call(x_local, (True, False), amax)
         return _ReduceFromGroup.apply(y, self.group)
 
 
@@ -146,7 +150,14 @@ class TensorParallelSwiGLU(nn.Module):
                    shard_cols(full_down, rank, world), group, linear_fn, device)
 
     def forward(self, x):
-        return self.down(F.silu(self.gate(x)) * self.up(x))
+        g, u = self.gate(x), self.up(x)
+        if self.gate.linear_fn is _fp4_linear_fn and g.is_cuda and g.dtype == torch.bfloat16:
+            # fused SwiGLU: the maxima it leaves are this rank's; the linears reduce them over the group
+            from .swiglu import swiglu
+            tokens = g.numel() // g.shape[-1]
+            h, h_max = swiglu(g, u, self.gate.signs if tokens % 16 == 0 else None)
+            return self.down(h, amax=h_max)
+        return self.down(F.silu(g) * u)
 
 
 # ------------------------------------------------------------------------------------------
