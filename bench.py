@@ -1,6 +1,6 @@
 """Benchmark of the NVFP4 hot path on B200.
 
-Headline line (one JSON object on stdout, rank 0): the fused quantizer on BASELINE config 2 --
+Headline line (one JSON object on stdout, rank 0): the fused quantizer on benchmark config 2 --
 a bf16 8192 x 4096 tensor (N(0,1) seed 1 + 0.1 % x50 outliers) quantized in three modes per step:
 round-to-nearest, stochastic rounding (Philox seed 7), and stochastic rounding after the 16-point
 random-sign Hadamard (sign seed 3).  metric = algorithmic HBM GB/s, bytes = M*K*(2 + 1/2 + 1/16)
@@ -412,7 +412,7 @@ def run_gpu_arm(args, rank, world, local_rank):
 
 
 def extras_tensor_parallel(Q, dev, rank, world, dist):
-    """BASELINE config 4 over `world` GPUs: SwiGLU d 4096 / h 14336 split column- (gate, up) and row-wise
+    """benchmark config 4 over `world` GPUs: SwiGLU d 4096 / h 14336 split column- (gate, up) and row-wise
     (down), 8 microbatches x 4096 tokens, forward + backward, amortized weight quantization; NCCL
     all-reduce of the amax words and of the row-parallel output / column-parallel input gradient.
     Strong scaling: the same total work on more GPUs.  Timed on the device, max over ranks."""
@@ -482,7 +482,7 @@ def extras_tensor_parallel(Q, dev, rank, world, dist):
 
 
 def extras(Q, dev, bf16_peak, peak_kind):
-    """Beside the headline: FP4 GEMM throughput on BASELINE config 3 shapes with bf16 torch.matmul
+    """Beside the headline: FP4 GEMM throughput on benchmark config 3 shapes with bf16 torch.matmul
     alongside, and the SwiGLU FFN of config 4 (d 4096, h 14336, 8 x 4096 tokens) forward+backward in
     FP4 (amortized weight quantization) against the same block in bf16."""
     out = {"gemm": []}

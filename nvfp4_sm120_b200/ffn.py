@@ -1,5 +1,5 @@
 """SwiGLU feed-forward block built from FP4Linear (or bf16 nn.Linear as the comparator): the FFN of
-BASELINE config 4 (d_model 4096, hidden 14336, three linears, Kaiming-uniform weights)."""
+benchmark config 4 (d_model 4096, hidden 14336, three linears, Kaiming-uniform weights)."""
 from __future__ import annotations
 
 import math

@@ -133,7 +133,7 @@ class RowParallelFP4Linear(_ParallelLinearBase):
 
 class TensorParallelSwiGLU(nn.Module):
     """SwiGLU FFN y = down(silu(gate(x)) * up(x)) with d_model d and hidden h, sharded over `group`
-    (BASELINE config 4: d 4096, h 14336).  Built from this rank's shards: gate/up [h/p, d], down [d, h/p];
+    (benchmark config 4: d 4096, h 14336).  Built from this rank's shards: gate/up [h/p, d], down [d, h/p];
     `from_full` slices them out of the unsharded [h, d], [h, d], [d, h] weights."""
 
     def __init__(self, gate_shard, up_shard, down_shard, group=None, linear_fn=None, device="cuda"):

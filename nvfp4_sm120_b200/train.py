@@ -1,4 +1,4 @@
-"""Training loop for the GPT of BASELINE config 5 on synthetic tokens, single GPU or data parallel.
+"""Training loop for the GPT of benchmark config 5 on synthetic tokens, single GPU or data parallel.
 
     python -m nvfp4_sm120_b200.train --steps 300 --backend fp4            # one GPU
     torchrun --nproc-per-node 8 -m nvfp4_sm120_b200.train --backend fp4   # data parallel over NCCL

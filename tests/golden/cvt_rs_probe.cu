@@ -43,7 +43,7 @@ int main(int argc,char**argv){
   std::vector<uint16_t> out(n); cudaError_t e=cudaMemcpy(out.data(),dout,n*2,cudaMemcpyDeviceToHost);
   printf("n=%d nstruct=%zu err=%s\n",n,nstruct,cudaGetErrorString(e));
   printf("order: in (0.5,1,2,4) -> 0x%04x ; (-0.5,1.5,-3,6) -> 0x%04x\n", out[0], out[1]);
-  FILE* f=fopen(argc>1?argv[1]:"gpurun_out/cvt_probe.bin","wb");
+  FILE* f=fopen(argc>1?argv[1]:"cvt_probe.bin","wb");
   fwrite(&n,4,1,f); fwrite(xs.data(),sizeof(float4),n,f); fwrite(rb.data(),4,n,f); fwrite(out.data(),2,n,f); fclose(f);
   return 0;
 }

@@ -78,7 +78,7 @@ def test_many_calls_reuse_workspace_without_leaking_state(Q):
 
 
 def test_full_size_round_trip_properties(Q):
-    """BASELINE config 2 size without a CPU oracle run: dequantised values stay within half a grid
+    """benchmark config 2 size without a CPU oracle run: dequantised values stay within half a grid
     step of the input (scaled), and quantising twice gives the same bytes (determinism)."""
     x = O.synthetic_tensor(8192, 4096, 1).cuda()
     a, b = Q.quant_nvfp4(x), Q.quant_nvfp4(x)

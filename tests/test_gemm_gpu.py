@@ -6,7 +6,7 @@ from oracle import nvfp4_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-REL_TOL = 1e-3        # BASELINE: within 1e-3 relative error of an fp32 matmul of the dequantised operands
+REL_TOL = 1e-3        # target: within 1e-3 relative error of an fp32 matmul of the dequantised operands
 
 
 @pytest.fixture(scope="module")
@@ -115,7 +115,7 @@ def test_gemm_bf16_out_is_rounded_fp32(Q):
 
 
 def test_config1_end_to_end(Q):
-    """BASELINE config 1 through fp4_matmul: A 2048x4096, B 4096x1024 (outliers x50)."""
+    """benchmark config 1 through fp4_matmul: A 2048x4096, B 4096x1024 (outliers x50)."""
     A = O.synthetic_tensor(2048, 4096, 0)
     B = O.synthetic_tensor(4096, 1024, 100)
     got = Q.fp4_matmul(A.cuda(), B.cuda(), out_dtype=torch.float32).cpu()

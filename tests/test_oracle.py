@@ -140,7 +140,7 @@ def test_philox_known_answers():
 
 
 def test_config1_tolerance_statement():
-    """BASELINE config 1 on a slice: RNE quantise -> dequantise, fp32 matmul; the
+    """benchmark config 1 on a slice: RNE quantise -> dequantise, fp32 matmul; the
     error against the unquantised product is the ~0.1 the reference reports."""
     A = O.synthetic_tensor(256, 512, 0)
     B = O.synthetic_tensor(512, 128, 1)

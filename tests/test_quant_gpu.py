@@ -51,7 +51,7 @@ def test_rne_reference_sweep_shapes(Q, shape):
 
 
 def test_config1_operands_bit_exact(Q):
-    """BASELINE config 1: A 2048x4096 and B 4096x1024 (quantised as B.t()), outliers x50."""
+    """benchmark config 1: A 2048x4096 and B 4096x1024 (quantised as B.t()), outliers x50."""
     A = O.synthetic_tensor(2048, 4096, 0)
     B = O.synthetic_tensor(4096, 1024, 100)
     _cmp(Q.quant_nvfp4(A.cuda()), O.quant_nvfp4(A), "A")
@@ -183,7 +183,7 @@ def test_argument_errors(Q):
 
 
 def test_full_size_properties(Q):
-    """BASELINE config 2 size (8192x4096): properties that need no CPU oracle run.  Every scale
+    """benchmark config 2 size (8192x4096): properties that need no CPU oracle run.  Every scale
     byte is a finite E4M3 in [2^-6, 448]; the per-tensor scale is amax / 2688; a stochastic draw
     keeps the scales and moves no nibble by more than one level."""
     x = O.synthetic_tensor(8192, 4096, 1).cuda()
