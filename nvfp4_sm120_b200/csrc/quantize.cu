@@ -316,6 +316,12 @@ extern "C" int nvfp4_amax_bf16(const void* x, int64_t rows, int64_t cols, int64_
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 
+namespace nvfp4 { namespace fused {
+int quantize_rows_known_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
+                             const float* signs16, const float* amax, uint64_t seed, uint64_t offset,
+                             uint8_t* qdata, uint8_t* scales, float* pts_out, cudaStream_t stream);
+}}
+
 extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
                                    int mode, int rht, const float* signs16, const float* amax,
                                    uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
@@ -332,6 +338,13 @@ extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, in
   const int64_t k = transpose ? rows : cols;
   if ((k & 15) != 0) return NVFP4_E_SHAPE;
   if (transpose && (cols & 1) != 0) return NVFP4_E_SHAPE;
+  if (!transpose) {
+    // row-wise output with the maximum given: one streaming pass of the single-launch kernel's
+    // quantize phase (it declines only tensors of 2^31 blocks or more, which the plain kernel takes)
+    const int rc = nvfp4::fused::quantize_rows_known_amax(x, rows, cols, ld, mode, rht, signs16, amax, seed, offset,
+                                                          qdata, scales, pts_out, stream);
+    if (rc != NVFP4_E_LIMIT) return rc;
+  }
   // padding of the tiled scale buffer must read as zero (the reference pads with zeros)
   const int64_t sm = (out_rows + 127) / 128 * 128, sk = (k / 16 + 3) / 4 * 4;
   if (sm != out_rows || sk != k / 16) {

@@ -165,7 +165,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_per_row, int64_t ld,
                    FastDiv div_bpr, const float* __restrict__ signs16, PhiloxKeys keys, uint64_t offset,
                    uint8_t* __restrict__ qdata, uint8_t* __restrict__ scales, float* __restrict__ pts_out,
-                   Workspace* __restrict__ ws, uint32_t blocks_per_cta, int contiguous) {
+                   Workspace* __restrict__ ws, uint32_t blocks_per_cta, int contiguous,
+                   const float* __restrict__ amax_in) {
+  // amax_in != nullptr: the caller knows the per-tensor maximum (a fused producer, or an all-reduce
+  // over a sharded tensor): no first pass, no grid barrier, no workspace; one streaming quantize pass.
+  const bool known = amax_in != nullptr;
   extern __shared__ __align__(128) uint8_t smem[];
   uint16_t* amax_tab = reinterpret_cast<uint16_t*>(smem + kStashBytes);       // bf16 bits, no RHT only
   float* recip_tab = reinterpret_cast<float*>(smem + kMiscOff);               // 128 floats
@@ -178,7 +182,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   const uint32_t b0 = min(total, blockIdx.x * blocks_per_cta);
   const uint32_t b1 = min(total, b0 + blocks_per_cta);
   // tail of the range that lives in shared memory (contiguous inputs only)
-  uint32_t stash_blocks = contiguous ? min(b1 - b0, (uint32_t)(kStashBytes / 32)) : 0u;
+  uint32_t stash_blocks = (contiguous && !known) ? min(b1 - b0, (uint32_t)(kStashBytes / 32)) : 0u;
   const uint32_t s0 = b1 - stash_blocks;                                      // first stashed block
   const uint32_t tid = threadIdx.x;
 
@@ -198,13 +202,13 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     }
   }
   if (RHT && tid < 16) sgs[tid] = __ldg(signs16 + tid);
-  const bool stamper = blockIdx.x == 0 && tid == 0;
+  const bool stamper = blockIdx.x == 0 && tid == 0 && ws != nullptr;
   unsigned long long t_start = 0;
   if (stamper) { t_start = global_ns(); ws->start = t_start; ws->last_end = 0ull; }
   // which of the two barrier slots this launch uses (needed only at the barrier: the load has all of
   // phase 1 to come back)
   unsigned int epoch = 0;
-  if (tid == 0) asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(&ws->epoch) : "memory");
+  if (tid == 0 && !known) asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(epoch) : "l"(&ws->epoch) : "memory");
   __syncthreads();
   uint32_t sm[8];                 // sign-bit masks of the packed bf16 pairs (bit 15: even, bit 31: odd)
 #pragma unroll
@@ -239,7 +243,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     return a;
   };
   // the streamed head, kBatch blocks per thread in flight before any of them is consumed
-  for (uint32_t i = b0 + tid; i < s0; i += kBatch * kThreads) {
+  for (uint32_t i = b0 + tid; i < s0 && !known; i += kBatch * kThreads) {
     uint32_t w[kBatch][8];
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
@@ -284,7 +288,9 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
   }
 
   // ------------------------------- grid barrier -------------------------------
-  if (tid < 32) {
+  if (known) {
+    if (tid == 0) red[0] = __ldg(amax_in);
+  } else if (tid < 32) {
     float mm = red[tid];
     mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 16));
     mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, 8));
@@ -345,7 +351,8 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
       amax_b *= 0.25f;                                   // H = butterfly / 4, an exact scaling
     } else {
       expand<false>(w, sm, v);
-      amax_b = (i - b0 < (uint32_t)kTabBlocks) ? __uint_as_float((uint32_t)amax_tab[i - b0] << 16) : amax_packed8(w);
+      amax_b = (!known && i - b0 < (uint32_t)kTabBlocks) ? __uint_as_float((uint32_t)amax_tab[i - b0] << 16)
+                                                         : amax_packed8(w);
     }
     const uint32_t sf = block_scale_byte(amax_b, sc);
     const float recip = RHT ? recip_tab[sf] * 0.25f : recip_tab[sf];
@@ -390,7 +397,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     load_stash(i, w);
     quantize(i, w);
   }
-  if (tid == 0) {                                                // diagnostics only, nothing waits for them
+  if (tid == 0 && ws != nullptr) {                               // diagnostics only, nothing waits for them
     const unsigned long long t_end = global_ns();
     if (stamper) ws->after[3] = (unsigned int)(t_end - t_start);
     atomicMax(&ws->last_end, t_end);
@@ -417,19 +424,11 @@ using namespace nvfp4::fused;
 
 extern "C" size_t nvfp4_quantize_fused_workspace_bytes(void) { return sizeof(Workspace); }
 
-extern "C" int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode,
-                                         int rht, const float* signs16, uint64_t seed, uint64_t offset,
-                                         uint8_t* qdata, uint8_t* scales, float* pts_out, void* workspace,
-                                         size_t workspace_bytes, void* stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  if (!x || !qdata || !scales || !workspace || (rht && !signs16)) return NVFP4_E_NULL;
-  if (workspace_bytes < sizeof(Workspace)) return NVFP4_E_WORKSPACE;
-  if (rows <= 0 || cols <= 0 || ld < cols || (cols & 15) != 0) return NVFP4_E_SHAPE;
-  if (rows * (cols / 16) >= (1ll << 31)) return NVFP4_E_LIMIT;
-  if (mode != NVFP4_ROUND_NEAREST && mode != NVFP4_ROUND_STOCHASTIC) return NVFP4_E_MODE;
-  auto mis = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
-  if (mis(x, 16) || (ld & 7) != 0 || mis(qdata, 16) || mis(scales, 16) || mis(workspace, 16)) return NVFP4_E_ALIGN;
-
+// Launch of the cooperative kernel.  amax_in == nullptr: two phases with the caller's workspace;
+// otherwise one quantize pass with the given per-tensor maximum (workspace unused, may be null).
+static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
+                        const float* signs16, uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
+                        float* pts_out, void* workspace, const float* amax_in, cudaStream_t stream) {
   static int sm_count[64] = {};
   static bool attr_done[64] = {};
   int dev = 0;
@@ -471,10 +470,48 @@ extern "C" int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t co
     keys.k[r][1] = (uint32_t)(seed >> 32) + (uint32_t)r * 0xBB67AE85u;
   }
   void* args[] = {&xp, &rows32, &bpr, &ld, &fd, &signs16, &keys, &offset, &qdata, &scales, &pts_out, &ws, &per,
-                  &contiguous};
+                  &contiguous, &amax_in};
   cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, kSmemBytes, stream);
   return e == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
+
+static int check_fused_args(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
+                            const float* signs16, const uint8_t* qdata, const uint8_t* scales) {
+  if (!x || !qdata || !scales || (rht && !signs16)) return NVFP4_E_NULL;
+  if (rows <= 0 || cols <= 0 || ld < cols || (cols & 15) != 0) return NVFP4_E_SHAPE;
+  if (rows * (cols / 16) >= (1ll << 31)) return NVFP4_E_LIMIT;
+  if (mode != NVFP4_ROUND_NEAREST && mode != NVFP4_ROUND_STOCHASTIC) return NVFP4_E_MODE;
+  auto mis = [](const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  if (mis(x, 16) || (ld & 7) != 0 || mis(qdata, 16) || mis(scales, 16)) return NVFP4_E_ALIGN;
+  return NVFP4_OK;
+}
+
+extern "C" int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode,
+                                         int rht, const float* signs16, uint64_t seed, uint64_t offset,
+                                         uint8_t* qdata, uint8_t* scales, float* pts_out, void* workspace,
+                                         size_t workspace_bytes, void* stream_) {
+  if (!workspace) return NVFP4_E_NULL;
+  if (workspace_bytes < sizeof(Workspace)) return NVFP4_E_WORKSPACE;
+  const int rc = check_fused_args(x, rows, cols, ld, mode, rht, signs16, qdata, scales);
+  if (rc != NVFP4_OK) return rc;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return NVFP4_E_ALIGN;
+  return launch_fused(x, rows, cols, ld, mode, rht, signs16, seed, offset, qdata, scales, pts_out, workspace, nullptr,
+                      static_cast<cudaStream_t>(stream_));
+}
+
+namespace nvfp4 { namespace fused {
+// For nvfp4_quantize_bf16 (row-wise output, maximum given): the same kernel as one streaming pass.
+// Returns NVFP4_E_LIMIT / NVFP4_E_ALIGN when this kernel does not take the case (the caller then
+// uses its plain kernel).
+int quantize_rows_known_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
+                             const float* signs16, const float* amax, uint64_t seed, uint64_t offset,
+                             uint8_t* qdata, uint8_t* scales, float* pts_out, cudaStream_t stream) {
+  const int rc = check_fused_args(x, rows, cols, ld, mode, rht, signs16, qdata, scales);
+  if (rc != NVFP4_OK) return rc;
+  return launch_fused(x, rows, cols, ld, mode, rht, signs16, seed, offset, qdata, scales, pts_out, nullptr, amax,
+                      stream);
+}
+}}
 
 // ---------------------------------------------------------------------------------------------
 // Variant for callers that cannot allocate device memory
