@@ -160,16 +160,19 @@ __device__ __forceinline__ void expand(const uint32_t (&w)[8], const uint32_t (&
   }
 }
 
-template <bool SR, bool RHT>
-__global__ void __launch_bounds__(kThreads, 1)
+// KNOWN: the per-tensor maximum comes in (amax_in), so the kernel is the quantize pass alone; that
+// variant runs 512 threads with 128 registers (the pass then streams from HBM and
+// needs the bytes in flight: two register buffers of three blocks per thread in turn).
+template <bool SR, bool RHT, bool KNOWN, int THREADS, int B2>
+__global__ void __launch_bounds__(THREADS, 1)
 quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_per_row, int64_t ld,
                    FastDiv div_bpr, const float* __restrict__ signs16, PhiloxKeys keys, uint64_t offset,
                    uint8_t* __restrict__ qdata, uint8_t* __restrict__ scales, float* __restrict__ pts_out,
                    Workspace* __restrict__ ws, uint32_t blocks_per_cta, int contiguous,
                    const float* __restrict__ amax_in) {
-  // amax_in != nullptr: the caller knows the per-tensor maximum (a fused producer, or an all-reduce
-  // over a sharded tensor): no first pass, no grid barrier, no workspace; one streaming quantize pass.
-  const bool known = amax_in != nullptr;
+  // KNOWN: the caller knows the per-tensor maximum (a fused producer, or an all-reduce over a
+  // sharded tensor): no first pass, no grid barrier, no workspace; one streaming quantize pass.
+  constexpr bool known = KNOWN;
   extern __shared__ __align__(128) uint8_t smem[];
   uint16_t* amax_tab = reinterpret_cast<uint16_t*>(smem + kStashBytes);       // bf16 bits, no RHT only
   float* recip_tab = reinterpret_cast<float*>(smem + kMiscOff);               // 128 floats
@@ -243,15 +246,15 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     return a;
   };
   // the streamed head, kBatch blocks per thread in flight before any of them is consumed
-  for (uint32_t i = b0 + tid; i < s0 && !known; i += kBatch * kThreads) {
+  for (uint32_t i = b0 + tid; i < s0 && !known; i += kBatch * THREADS) {
     uint32_t w[kBatch][8];
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
-      const uint32_t iu = min(i + u * kThreads, s0 - 1);     // clamped duplicates cost no extra traffic
+      const uint32_t iu = min(i + u * THREADS, s0 - 1);     // clamped duplicates cost no extra traffic
       load_global(iu, w[u]);
     }
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) m = fmaxf(m, block_max(min(i + u * kThreads, s0 - 1), w[u]));
+    for (int u = 0; u < kBatch; ++u) m = fmaxf(m, block_max(min(i + u * THREADS, s0 - 1), w[u]));
   }
   if (stamper) ws->after[0] = (unsigned int)(global_ns() - t_start);
   if (stash_blocks > 0) {
@@ -263,7 +266,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
       }
     }
     if (!landed) { *cta_abort = 1; ws->error = 2; }
-    for (uint32_t i = s0 + tid; i < b1; i += kThreads) {
+    for (uint32_t i = s0 + tid; i < b1; i += THREADS) {
       uint32_t w[8];
       load_stash(i, w);
       m = fmaxf(m, block_max(i, w));
@@ -280,11 +283,11 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
 
   // The first blocks of the quantize pass do not depend on the maximum: their loads (L2 hits by now)
   // go out before the barrier and are in registers when it opens.
-  uint32_t pre[kBatch2][8];
+  uint32_t pre[B2][8];
   const uint32_t i_first = b0 + tid;
   if (i_first < s0) {
 #pragma unroll
-    for (int u = 0; u < kBatch2; ++u) load_global(min(i_first + u * kThreads, s0 - 1), pre[u]);
+    for (int u = 0; u < B2; ++u) load_global(min(i_first + u * THREADS, s0 - 1), pre[u]);
   }
 
   // ------------------------------- grid barrier -------------------------------
@@ -375,24 +378,41 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     const uint32_t tile = (r >> 7) * col_tiles + (kb >> 2);
     scales[(size_t)tile * 512 + ((r & 31u) << 4) + (((r >> 5) & 3u) << 2) + (kb & 3u)] = (uint8_t)sf;
   };
-  // the streamed head out of the L2 (first batch already loaded), then the stashed tail
-  if (i_first < s0) {
+  // the streamed head (first batch already loaded), then the stashed tail
+  auto load_batch = [&](uint32_t i, uint32_t (&w)[B2][8]) {
 #pragma unroll
-    for (int u = 0; u < kBatch2; ++u)
-      if (i_first + u * kThreads < s0) quantize(i_first + u * kThreads, pre[u]);
-  }
-  for (uint32_t i = i_first + kBatch2 * kThreads; i < s0; i += kBatch2 * kThreads) {
-    uint32_t w[kBatch2][8];
+    for (int u = 0; u < B2; ++u) load_global(min(i + u * THREADS, s0 - 1), w[u]);
+  };
+  auto quantize_batch = [&](uint32_t i, const uint32_t (&w)[B2][8]) {
 #pragma unroll
-    for (int u = 0; u < kBatch2; ++u) {
-      const uint32_t iu = min(i + u * kThreads, s0 - 1);
-      load_global(iu, w[u]);
+    for (int u = 0; u < B2; ++u)
+      if (i + u * THREADS < s0) quantize(i + u * THREADS, w[u]);
+  };
+  if (KNOWN) {
+    // out of HBM: the loads of the next batch are in flight while this one is encoded (two register
+    // buffers in turn; this variant has the registers for it)
+    uint32_t nxt[B2][8];
+    uint32_t i = i_first;
+    while (i < s0) {
+      uint32_t in = i + B2 * THREADS;
+      if (in < s0) load_batch(in, nxt);
+      quantize_batch(i, pre);
+      i = in;
+      if (i >= s0) break;
+      in = i + B2 * THREADS;
+      if (in < s0) load_batch(in, pre);
+      quantize_batch(i, nxt);
+      i = in;
     }
-#pragma unroll
-    for (int u = 0; u < kBatch2; ++u)
-      if (i + u * kThreads < s0) quantize(i + u * kThreads, w[u]);
+  } else {
+    if (i_first < s0) quantize_batch(i_first, pre);
+    for (uint32_t i = i_first + B2 * THREADS; i < s0; i += B2 * THREADS) {
+      uint32_t w[B2][8];
+      load_batch(i, w);
+      quantize_batch(i, w);
+    }
   }
-  for (uint32_t i = s0 + tid; i < b1; i += kThreads) {
+  for (uint32_t i = s0 + tid; i < b1; i += THREADS) {
     uint32_t w[8];
     load_stash(i, w);
     quantize(i, w);
@@ -437,11 +457,22 @@ static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, i
       cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
     return NVFP4_E_LAUNCH;
   const bool sr = mode == NVFP4_ROUND_STOCHASTIC;
-  const void* fn = sr ? (rht ? (const void*)quant_fused_kernel<true, true> : (const void*)quant_fused_kernel<true, false>)
-                      : (rht ? (const void*)quant_fused_kernel<false, true> : (const void*)quant_fused_kernel<false, false>);
+  const bool known = amax_in != nullptr;
+  constexpr int kThreadsKnown = 512, kBatchKnown = 3;
+#define NVFP4_FUSED_FN(K_, T_, B_) \
+  (sr ? (rht ? (const void*)quant_fused_kernel<true, true, K_, T_, B_> : (const void*)quant_fused_kernel<true, false, K_, T_, B_>) \
+      : (rht ? (const void*)quant_fused_kernel<false, true, K_, T_, B_> : (const void*)quant_fused_kernel<false, false, K_, T_, B_>))
+  const void* fn = known ? NVFP4_FUSED_FN(true, kThreadsKnown, kBatchKnown) : NVFP4_FUSED_FN(false, kThreads, kBatch2);
+#undef NVFP4_FUSED_FN
   if (!attr_done[dev]) {
-    const void* all[4] = {(const void*)quant_fused_kernel<true, true>, (const void*)quant_fused_kernel<true, false>,
-                          (const void*)quant_fused_kernel<false, true>, (const void*)quant_fused_kernel<false, false>};
+    const void* all[8] = {(const void*)quant_fused_kernel<true, true, false, kThreads, kBatch2>,
+                          (const void*)quant_fused_kernel<true, false, false, kThreads, kBatch2>,
+                          (const void*)quant_fused_kernel<false, true, false, kThreads, kBatch2>,
+                          (const void*)quant_fused_kernel<false, false, false, kThreads, kBatch2>,
+                          (const void*)quant_fused_kernel<true, true, true, kThreadsKnown, kBatchKnown>,
+                          (const void*)quant_fused_kernel<true, false, true, kThreadsKnown, kBatchKnown>,
+                          (const void*)quant_fused_kernel<false, true, true, kThreadsKnown, kBatchKnown>,
+                          (const void*)quant_fused_kernel<false, false, true, kThreadsKnown, kBatchKnown>};
     for (const void* f : all)
       if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
         return NVFP4_E_LAUNCH;
@@ -471,7 +502,7 @@ static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, i
   }
   void* args[] = {&xp, &rows32, &bpr, &ld, &fd, &signs16, &keys, &offset, &qdata, &scales, &pts_out, &ws, &per,
                   &contiguous, &amax_in};
-  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, kSmemBytes, stream);
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(known ? kThreadsKnown : kThreads), args, kSmemBytes, stream);
   return e == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 
