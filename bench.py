@@ -501,6 +501,10 @@ def extras(Q, dev, bf16_peak, peak_kind):
             torch.matmul(A, Bt.t(), out=d)
         res = {}
         for name, fn in (("fp4", fp4), ("bf16", bf16)):
+            # single launches are burst numbers: let the previous shape's seconds of dense GEMMs drain
+            # out of the power/thermal state first (the last shape read 30 % low right after 16384^3)
+            torch.cuda.synchronize()
+            time.sleep(1.0)
             for i in range(3):
                 fn(i)
             ts = []
