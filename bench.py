@@ -399,9 +399,15 @@ def run_gpu_arm(args, rank, world, local_rank):
                                 "cores": cores, "kind": "port",
                                 "sample": f"{rows} of {ROWS} rows x {COLS} cols, three modes, best of 2"}
         if not args.no_extras:
-            line["extras"] = extras(Q, dev, bf16_peak, peak_kind)
+            try:                                   # what stands beside the headline must not take it down
+                line["extras"] = extras(Q, dev, bf16_peak, peak_kind)
+            except Exception as exc:
+                line["extras"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     if world > 1 and not args.no_extras:
-        tp = extras_tensor_parallel(Q, dev, rank, world, dist)
+        try:
+            tp = extras_tensor_parallel(Q, dev, rank, world, dist)
+        except Exception as exc:
+            tp = {"error": f"{type(exc).__name__}: {exc}"[:300]}
         if rank == 0:
             line["extras"] = {"ffn_tensor_parallel": tp}
     if rank == 0:
