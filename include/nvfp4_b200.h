@@ -174,6 +174,19 @@ int nvfp4_swiglu_bwd_bf16(const void* gate, const void* up, const void* dout, in
                           int64_t ld_in, void* dgate, void* dup, int64_t ld_out, const float* signs16,
                           float* maxima4, int zero_first, void* stream);
 
+/*
+ * The same producer fusion for the squared-ReLU MLP of the reference's models
+ * (nvfp4_train.py:120-123): out = relu(x)^2, and backward dx = 2 relu(x) * dout, each with
+ * maxima2 = {max|result|, max|RHT_rows(result)|} as above.  Only for 16-byte rows (cols, ld_in,
+ * ld_out multiples of 8, 16-byte aligned pointers); NVFP4_E_ALIGN otherwise.  No fused
+ * counterpart in the reference (torch element-wise kernels there).
+ */
+int nvfp4_relu2_fwd_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld_in, void* out, int64_t ld_out,
+                         const float* signs16, float* maxima2, int zero_first, void* stream);
+int nvfp4_relu2_bwd_bf16(const void* x, const void* dout, int64_t rows, int64_t cols, int64_t ld_in,
+                         void* dx, int64_t ld_out, const float* signs16, float* maxima2, int zero_first,
+                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -336,6 +336,63 @@ __global__ void __launch_bounds__(256) swiglu_bwd_wide_kernel(const uint16_t* __
   cta_max_to_global<4>(m, maxima, use);
 }
 
+// Squared ReLU, the MLP activation of the reference's models (nvfp4_train.py:120-123,
+// scaling/train_text.py:57-59): a = relu(x)^2 and da/dx = 2 relu(x), with the same two maxima of what
+// is written.  Same tiling as the wide SwiGLU kernels; BWD reads x and the incoming gradient.
+template <bool BWD>
+__global__ void __launch_bounds__(256) relu2_wide_kernel(const uint16_t* __restrict__ x,
+                                                         const uint16_t* __restrict__ dout, int64_t rows,
+                                                         int64_t cols, int64_t ld_in, uint16_t* __restrict__ out,
+                                                         int64_t ld_out, const float* __restrict__ signs16,
+                                                         float* __restrict__ maxima) {
+  __shared__ __align__(16) uint32_t tile[16 * kPitchWords];
+  const bool rht = signs16 != nullptr;
+  float sg[16];
+  if (rht) load_signs(signs16, sg);
+  const int64_t c0 = (int64_t)blockIdx.x * kTileCols;
+  const int cc = (threadIdx.x & 63) * 8;
+  const bool col_in = c0 + cc < cols;
+  float m[2] = {0.0f, 0.0f};
+#pragma unroll 1
+  for (int j = 0; j < kRowBlocks; ++j) {
+    const int64_t r0 = ((int64_t)blockIdx.y * kRowBlocks + j) * 16;
+    if (r0 >= rows) break;
+    uint4 x4[4], d4[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int64_t r = r0 + 4 * k + (threadIdx.x >> 6);
+      const bool in = col_in && r < rows;
+      x4[k] = in ? ldg16(x + r * ld_in + c0 + cc) : make_uint4(0, 0, 0, 0);
+      if (BWD) d4[k] = in ? ldg16(dout + r * ld_in + c0 + cc) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t xw[4] = {x4[k].x, x4[k].y, x4[k].z, x4[k].w};
+      const uint32_t dw[4] = {BWD ? d4[k].x : 0u, BWD ? d4[k].y : 0u, BWD ? d4[k].z : 0u, BWD ? d4[k].w : 0u};
+      uint32_t hw[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float r0f = fmaxf(bf16_lo(xw[q]), 0.0f), r1f = fmaxf(bf16_hi(xw[q]), 0.0f);
+        hw[q] = BWD ? pack_bf16x2(2.0f * r0f * bf16_lo(dw[q]), 2.0f * r1f * bf16_hi(dw[q]))
+                    : pack_bf16x2(r0f * r0f, r1f * r1f);
+        m[0] = fmaxf(m[0], fmaxf(fabsf(bf16_lo(hw[q])), fabsf(bf16_hi(hw[q]))));
+      }
+      const int rl = 4 * k + (threadIdx.x >> 6);
+      const int64_t r = r0 + rl;
+      const uint4 h4 = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+      if (col_in && r < rows) *reinterpret_cast<uint4*>(out + r * ld_out + c0 + cc) = h4;
+      if (rht) *reinterpret_cast<uint4*>(&tile[rl * kPitchWords + (cc >> 1)]) = h4;
+    }
+    if (rht) {
+      __syncthreads();
+      tile_rht_max(tile, sg, c0 + 2 * (int64_t)threadIdx.x < cols, m[1]);
+      __syncthreads();
+    }
+  }
+  const bool use[2] = {true, rht};
+  cta_max_to_global<2>(m, maxima, use);
+}
+
 // 16-byte rows everywhere: the wide kernels apply
 static bool wide_ok(const void* a, const void* b, const void* c, const void* o1, const void* o2, int64_t cols,
                     int64_t ld_in, int64_t ld_out) {
@@ -399,5 +456,37 @@ extern "C" int nvfp4_swiglu_bwd_bf16(const void* gate, const void* up, const voi
                                                  static_cast<const uint16_t*>(dh), rows, cols, ld_in,
                                                  static_cast<uint16_t*>(dgate), static_cast<uint16_t*>(dup), ld_out,
                                                  signs16, maxima4);
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+
+// Squared ReLU and its backward with the maxima of the result (see relu2_wide_kernel).  Rows of 16
+// bytes only (cols and both leading dimensions multiples of 8, 16-byte aligned pointers): other
+// layouts get NVFP4_E_ALIGN and the caller keeps its own element-wise path.
+extern "C" int nvfp4_relu2_fwd_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld_in, void* out,
+                                    int64_t ld_out, const float* signs16, float* maxima2, int zero_first,
+                                    void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int rc = check(x, x, x, out, out, rows, cols, ld_in, ld_out, signs16, maxima2);
+  if (rc != NVFP4_OK) return rc;
+  if (!wide_ok(x, x, x, out, out, cols, ld_in, ld_out)) return NVFP4_E_ALIGN;
+  if (zero_first && cudaMemsetAsync(maxima2, 0, 2 * sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
+  const dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
+  relu2_wide_kernel<false><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), nullptr, rows, cols, ld_in,
+                                                      static_cast<uint16_t*>(out), ld_out, signs16, maxima2);
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+
+extern "C" int nvfp4_relu2_bwd_bf16(const void* x, const void* dout, int64_t rows, int64_t cols, int64_t ld_in,
+                                    void* dx, int64_t ld_out, const float* signs16, float* maxima2, int zero_first,
+                                    void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int rc = check(x, dout, x, dx, dx, rows, cols, ld_in, ld_out, signs16, maxima2);
+  if (rc != NVFP4_OK) return rc;
+  if (!wide_ok(x, dout, x, dx, dx, cols, ld_in, ld_out)) return NVFP4_E_ALIGN;
+  if (zero_first && cudaMemsetAsync(maxima2, 0, 2 * sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
+  const dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
+  relu2_wide_kernel<true><<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), static_cast<const uint16_t*>(dout),
+                                                     rows, cols, ld_in, static_cast<uint16_t*>(dx), ld_out, signs16,
+                                                     maxima2);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }

@@ -13,7 +13,8 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .linear import make_linear
+from .linear import FP4Linear, make_linear
+from .swiglu import relu2
 
 
 @dataclass
@@ -56,6 +57,9 @@ class DecoderBlock(nn.Module):
         self.o = make_linear(dim, dim, use_fp4, device)
         self.up = make_linear(dim, hidden, use_fp4, device)
         self.down = make_linear(hidden, dim, use_fp4, device)
+        # the fused activation computes the Hadamard maxima for `down` and for `up`'s gradient with one
+        # sign vector: both linears must hold the same one (they do unless a checkpoint changed them)
+        self.fused_act = bool(use_fp4 and torch.equal(self.up.signs, self.down.signs))
 
     def forward(self, x, cos, sin):
         B, T, _ = x.shape
@@ -68,7 +72,13 @@ class DecoderBlock(nn.Module):
             k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
         att = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.o(att.transpose(1, 2).reshape(B, T, -1))
-        return x + self.down(F.relu(self.up(self.norm_mlp(x))).square())
+        u = self.up(self.norm_mlp(x))
+        if (self.fused_act and isinstance(self.down, FP4Linear) and u.is_cuda and u.dtype == torch.bfloat16
+                and u.shape[-1] % 8 == 0):
+            # fused relu^2 that also hands `down` the maxima of its input (and `up` those of its gradient)
+            a, a_max = relu2(u, self.down.signs if (B * T) % 16 == 0 else None)
+            return x + self.down(a, amax=a_max)
+        return x + self.down(F.relu(u).square())
 
 
 class GPT(nn.Module):

@@ -65,3 +65,50 @@ class SwiGLUFn(torch.autograd.Function):
 def swiglu(g, u, signs=None):
     """h = silu(g) * u and the maxima of h (see SwiGLUFn)."""
     return SwiGLUFn.apply(g, u, signs)
+
+
+class ReLU2Fn(torch.autograd.Function):
+    """x -> (relu(x)^2, maxima): the MLP activation of the reference's models (nvfp4_train.py:120-123)
+    fused with the maxima of its result, like SwiGLUFn; the backward hints the maxima of dx to the
+    linear that produced x."""
+
+    @staticmethod
+    def forward(ctx, x, signs):
+        if x.dtype != torch.bfloat16 or x.shape[-1] % 8 != 0:
+            raise ValueError("fused squared ReLU takes a bf16 tensor whose last dimension is a multiple of 8")
+        x2 = _rows(x).contiguous()
+        rows, cols = x2.shape
+        use_rht = signs is not None and rows % 16 == 0
+        sg = _signs(signs, x.device) if use_rht else None
+        out = torch.empty_like(x2)
+        maxima = torch.empty(2, dtype=torch.float32, device=x.device)
+        code = _lib.lib().nvfp4_relu2_fwd_bf16(x2.data_ptr(), rows, cols, x2.stride(0), out.data_ptr(), out.stride(0),
+                                               sg.data_ptr() if use_rht else None, maxima.data_ptr(), 1, _stream())
+        _lib.check(code, "nvfp4_relu2_fwd_bf16")
+        ctx.save_for_backward(x2)
+        ctx.sg, ctx.use_rht, ctx.shape = sg, use_rht, x.shape
+        ctx.mark_non_differentiable(maxima)
+        return out.reshape(x.shape), maxima
+
+    @staticmethod
+    def backward(ctx, dout, _dmax):
+        (x2,) = ctx.saved_tensors
+        d2 = _rows(dout)
+        if d2.dtype != torch.bfloat16:
+            d2 = d2.to(torch.bfloat16)
+        d2 = d2.contiguous()
+        rows, cols = x2.shape
+        dx = torch.empty_like(x2)
+        maxima = torch.empty(2, dtype=torch.float32, device=x2.device)
+        code = _lib.lib().nvfp4_relu2_bwd_bf16(x2.data_ptr(), d2.data_ptr(), rows, cols, x2.stride(0), dx.data_ptr(),
+                                               dx.stride(0), ctx.sg.data_ptr() if ctx.use_rht else None,
+                                               maxima.data_ptr(), 1, _stream())
+        _lib.check(code, "nvfp4_relu2_bwd_bf16")
+        dx = dx.reshape(ctx.shape)
+        _linear.hint_grad_amax(dx, maxima, ctx.use_rht)
+        return dx, None
+
+
+def relu2(x, signs=None):
+    """relu(x)^2 and the maxima of the result (see ReLU2Fn)."""
+    return ReLU2Fn.apply(x, signs)

@@ -134,3 +134,55 @@ def test_narrow_kernels_match_wide_kernels(Q):
     assert torch.equal(h0, h1) and torch.equal(dg0, dg1) and torch.equal(du0, du1)
     assert torch.equal(_bits(mx0), _bits(mx1))
     assert all(torch.equal(_bits(a), _bits(b)) for a, b in zip(hint0, hint1))
+
+
+@pytest.mark.parametrize("shape", [(16, 32), (512, 3072), (40, 64)])
+def test_relu2_values_maxima_and_hint(Q, shape):
+    from nvfp4_sm120_b200 import linear, quant
+    from nvfp4_sm120_b200.swiglu import relu2
+    from oracle import nvfp4_oracle as O
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.randn(*shape, device="cuda", generator=gen).to(torch.bfloat16).requires_grad_(True)
+    d = torch.randn(*shape, device="cuda", generator=gen).to(torch.bfloat16)
+    signs = O.signs_from_seed(3).cuda()
+    has_rht = shape[0] % 16 == 0
+    linear._GRAD_AMAX.clear()
+    a, mx = relu2(x, signs)
+    (dx,) = torch.autograd.grad(a, [x], grad_outputs=d)
+    xf = x.detach().float()
+    assert torch.equal(a, (torch.relu(xf) ** 2).to(torch.bfloat16))                 # one rounding of an exact product
+    assert torch.equal(dx, (2 * torch.relu(xf) * d.float()).to(torch.bfloat16))
+    assert torch.equal(_bits(mx[0:1]), _bits(quant.tensor_amax(a)))
+    plain, rht = linear._take_grad_amax(dx.reshape(-1, dx.shape[-1]))
+    assert torch.equal(_bits(plain), _bits(quant.tensor_amax(dx)))
+    if has_rht:
+        assert torch.equal(_bits(mx[1:2]), _bits(quant.tensor_amax(a, rht=True, signs=signs, transpose=True)))
+        assert torch.equal(_bits(rht), _bits(quant.tensor_amax(dx, rht=True, signs=signs, transpose=True)))
+    else:
+        assert rht is None and float(mx[1]) == 0.0
+
+
+def test_decoder_block_fused_activation_matches_torch_ops(Q):
+    """The GPT block with the fused relu^2 against the same block with torch element-wise ops: same
+    weights and stochastic-rounding seeds; relu^2 is exact in fp32, so only bf16-ulp effects remain."""
+    from nvfp4_sm120_b200 import quant
+    from nvfp4_sm120_b200.models import DecoderBlock, rotary_tables
+    Q.set_amortize(False)
+    torch.manual_seed(0)
+    blk = DecoderBlock(256, 4, 4, 1024, True, "cuda")
+    assert blk.fused_act
+    x = torch.randn(2, 64, 256, device="cuda")
+    cos, sin = rotary_tables(64, 64, "cuda")
+    outs = []
+    for fused in (True, False):
+        blk.fused_act = fused
+        quant._SEED[0] = 500
+        xi = x.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = blk(xi, cos, sin)
+        g = torch.autograd.grad(y.float().square().mean(), [xi] + list(blk.parameters()))
+        outs.append((y, g))
+    (ya, ga), (yb, gb) = outs
+    rel = lambda p, q: ((p.float() - q.float()).norm() / (q.float().norm() + 1e-30)).item()
+    assert rel(ya, yb) < 2e-2
+    assert all(rel(p, q) < 0.15 for p, q in zip(ga, gb))
