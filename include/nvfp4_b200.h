@@ -119,12 +119,26 @@ int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t cols, int64_t
  *   - All calls on a device share the array: calls that can overlap on the GPU (different
  *     streams) race on it.  Calls on one stream are safe; each call clears what it needs.
  *   - Limit: rows * cols / 16 <= 2^31 - 1, otherwise NVFP4_E_LIMIT.
+ *   - A bounded wait inside the kernel that gives up (outputs then undefined) sets an error word in
+ *     the library's array; the call itself has long returned NVFP4_OK by then.  The word stays set
+ *     across later calls until nvfp4_quantize_static_status reads and clears it.
  * This entry point has no counterpart in the reference.
  */
 int nvfp4_quantize_static_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
                                int mode, int rht, const float* signs16,
                                uint64_t philox_seed, uint64_t philox_offset,
                                uint8_t* qdata, uint8_t* scales, float* pts_out, void* stream);
+
+/*
+ * Error word of nvfp4_quantize_static_bf16 on the current device, copied to *host_out (HOST
+ * pointer): 0 = every call since the last clear ran to its end, 1 = a grid barrier gave up,
+ * 2 = a bulk copy never landed.  The copy is enqueued on `stream` behind the calls already there,
+ * and this function waits for it (cudaStreamSynchronize), so *host_out is valid on return; with
+ * clear != 0 the word is zeroed behind the copy.  Allocates nothing.  Do not call it during stream
+ * capture.  No counterpart in the reference (the workspace entry point exposes the same word as
+ * int32 word 4 of the caller's workspace).
+ */
+int nvfp4_quantize_static_status(int32_t* host_out, int clear, void* stream);
 
 /*
  * Block-scaled FP4 GEMM  D[M, N] = (A . sfA) (B . sfB)^T * (*a_pts) * (*b_pts)
@@ -144,9 +158,8 @@ int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
 
 /*
  * Kernel choice of nvfp4_gemm for this process: 0 = automatic (the default), 1 = always the
- * one-CTA 128x256 kernel, 2 = always the two-CTA 256x256 kernel with one tile per cluster, 3 =
- * always the persistent two-CTA kernel.  For tuning and tests; results are the same to rounding
- * of the accumulation order.  No counterpart in the reference.
+ * one-CTA 128x256 kernel, 2 = always the persistent two-CTA 256x256 kernel.  For tuning and tests;
+ * results are the same to rounding of the accumulation order.  No counterpart in the reference.
  */
 int nvfp4_gemm_set_mode(int mode);
 

@@ -27,6 +27,7 @@ _SIGS = {
     "nvfp4_quantize_static_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
                                               _c.c_void_p, _c.c_uint64, _c.c_uint64, _c.c_void_p, _c.c_void_p,
                                               _c.c_void_p, _c.c_void_p]),
+    "nvfp4_quantize_static_status": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p]),
     "nvfp4_swiglu_fwd_bf16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p,
                                          _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nvfp4_swiglu_bwd_bf16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64,
@@ -73,3 +74,22 @@ def check(code, what):
     if code != OK:
         msg = lib().nvfp4_status_string(code).decode()
         raise NVFP4Error(f"{what} failed: {msg} (code {code})")
+
+
+def cuda_device_of(*tensors):
+    """The one CUDA device all `tensors` live on.  Raises NVFP4Error for a CPU tensor or for
+    operands on different devices: the C side launches on the CURRENT device with the pointers it
+    is given, so the wrappers make the operands' device current around every call."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if t.device.type != "cuda":
+            raise NVFP4Error(f"expected CUDA tensors, got one on {t.device} (there is no CPU path)")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise NVFP4Error(f"operands on different devices: {dev} and {t.device}")
+    if dev is None:
+        raise NVFP4Error("no tensor operand")
+    return dev

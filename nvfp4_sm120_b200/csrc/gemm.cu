@@ -14,7 +14,9 @@
 //               store bf16/fp32
 // All waits are bounded: a wait that gives up writes a code to *status, raises a CTA-wide abort
 // flag, and the kernel drains and frees its tensor memory before returning.
-// gemm_2cta.cu holds the cta_group::2 variant (256 x 256 per CTA pair) and the C entry point.
+// gemm_pair.cu holds the persistent cta_group::2 kernel (256 x 256 per CTA pair), gemm_api.cu the C entry point.
+#include <atomic>
+
 #include "gemm_common.cuh"
 
 namespace nvfp4 {
@@ -234,13 +236,13 @@ namespace nvfp4 { namespace gemm {
 // launch of the one-CTA kernel (arguments already validated)
 int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const Params& p,
                 cudaStream_t stream) {
-  static bool attr_set[64] = {};
+  static std::atomic<bool> attr_set[64];        // setting the attribute twice is harmless; the flag is atomic
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
-  if (!attr_set[dev]) {
+  if (!attr_set[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return NVFP4_E_LAUNCH;
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   const int64_t n_tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + kTileM - 1) / kTileM);
   if (n_tiles * p.splits > 0x7fffffffLL) return NVFP4_E_SHAPE;

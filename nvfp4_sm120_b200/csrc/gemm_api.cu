@@ -1,10 +1,6 @@
 // nvfp4_gemm: argument checks, tensor maps, kernel choice (C ABI; declared in include/nvfp4_b200.h).
 #include "gemm_common.cuh"
 
-namespace nvfp4 { namespace gemm2 {
-int launch_2cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const gemm::Params& p,
-                cudaStream_t stream);
-}}
 namespace nvfp4 { namespace gemm3 {
 int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const gemm::Params& p,
                 cudaStream_t stream);
@@ -14,16 +10,18 @@ int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtens
                 cudaStream_t stream);
 }}
 
-static int g_gemm_mode = 0;
+#include <atomic>
+
+static std::atomic<int> g_gemm_mode{0};
 extern "C" int nvfp4_gemm_set_mode(int mode) {
-  if (mode < 0 || mode > 3) return NVFP4_E_MODE;
-  g_gemm_mode = mode;
+  if (mode < 0 || mode > 2) return NVFP4_E_MODE;
+  g_gemm_mode.store(mode, std::memory_order_relaxed);
   return NVFP4_OK;
 }
 
-// Automatic choice: the persistent pair kernel (mode 3), which measured fastest on every shape with
-// more than one row tile; the one-CTA kernel when M <= 128 (a pair would compute 128 rows of padding)
-// and for the split-K case below.  Modes 1-3 force a kernel, for tuning and tests.
+// Automatic choice: the persistent pair kernel (mode 2), which measured fastest on every shape with
+// more than one row tile; the one-CTA kernel (mode 1) when M <= 128 (a pair would compute 128 rows of
+// padding) and for the split-K case below.  Modes 1 and 2 force a kernel, for tuning and tests.
 extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
                           const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
                           int64_t K, int64_t ldd, int32_t* status, void* stream_) {
@@ -38,8 +36,9 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
   // split K (one-CTA kernel only, see below) when a small fp32 output would leave most SMs idle
   const int64_t tiles_1cta = ((N + 255) / 256) * ((M + 127) / 128), slices = (K + 255) / 256;
   const bool want_split = out_dtype == NVFP4_OUT_F32 && tiles_1cta <= 74 && slices >= 16;
-  const int mode = g_gemm_mode != 0 ? g_gemm_mode : ((M > 128 && !want_split) ? 3 : 1);
-  const bool pair = mode >= 2;
+  const int forced = g_gemm_mode.load(std::memory_order_relaxed);
+  const int mode = forced != 0 ? forced : ((M > 128 && !want_split) ? 2 : 1);
+  const bool pair = mode == 2;
   CUtensorMap map_a, map_b;
   if (!make_operand_map(&map_a, a_q, M, K, 128) || !make_operand_map(&map_b, b_q, N, K, pair ? 128 : 256))
     return NVFP4_E_DRIVER;
@@ -67,6 +66,5 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
     if (!make_output_map(&map_d, d, M, N, ldd, p.out_f32 != 0)) return NVFP4_E_DRIVER;
     p.tma_store = 1;
   }
-  if (mode == 3) return nvfp4::gemm3::launch_pair(map_a, map_b, map_d, p, stream);
-  return pair ? nvfp4::gemm2::launch_2cta(map_a, map_b, map_d, p, stream) : launch_1cta(map_a, map_b, map_d, p, stream);
+  return pair ? nvfp4::gemm3::launch_pair(map_a, map_b, map_d, p, stream) : launch_1cta(map_a, map_b, map_d, p, stream);
 }

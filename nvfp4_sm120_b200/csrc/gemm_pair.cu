@@ -7,13 +7,15 @@
 //               copies of the scale tiles, into a ring of five stages that runs on across tiles;
 //   warp 1      (leader CTA only) issues tcgen05.mma cta_group::2, M 256 = 128 per CTA, N 256, K 64:
 //               four per K slice, back to back, one barrier wait per slice;
-//   warps 2-9   two sets of four: scale factors shared memory -> registers -> tensor memory;
-//   warps 10-17 epilogue: tensor memory -> registers -> swizzled shared memory -> TMA store.
+//   warps 2-5   scale factors shared memory -> registers -> tensor memory (one warp per 32-lane quarter);
+//   warps 6-13  epilogue: tensor memory -> registers -> swizzled shared memory -> TMA store.
 // Because the ring never drains, the loads of the next tile are in flight while the epilogue warps
 // empty the accumulator; the MMA issuer only waits for "accumulator read" before the next tile, so
 // the launch, barrier set-up, tensor-memory allocation and pipeline fill are paid once per SM pair,
 // not once per tile.  All waits are bounded (they raise the status word and every role leaves its
 // loops); the kernel ends with a cluster barrier before the paired tensor-memory free.
+#include <atomic>
+
 #include "gemm_common.cuh"
 
 namespace nvfp4 {
@@ -388,20 +390,20 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
 
 int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const Params& p,
                 cudaStream_t stream) {
-  static bool attr_set[64] = {};
-  static int sm_count[64] = {};
+  static std::atomic<int> sm_count[64];         // 0 = not looked up yet; a second look-up is harmless
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
-  if (!attr_set[dev]) {
+  int sms = sm_count[dev].load(std::memory_order_acquire);
+  if (sms == 0) {
     if (cudaFuncSetAttribute(gemm3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
       return NVFP4_E_LAUNCH;
-    if (cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count[dev] < 2)
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms < 2)
       return NVFP4_E_LAUNCH;
-    attr_set[dev] = true;
+    sm_count[dev].store(sms, std::memory_order_release);
   }
   const int64_t tiles = ((p.N + kTileN - 1) / kTileN) * ((p.M + 255) / 256);
   if (tiles > 0x3fffffffLL) return NVFP4_E_SHAPE;
-  const int64_t clusters = tiles < sm_count[dev] / 2 ? tiles : sm_count[dev] / 2;    // one resident pair per two SMs
+  const int64_t clusters = tiles < sms / 2 ? tiles : sms / 2;    // one resident pair per two SMs
   gemm3_kernel<<<dim3((unsigned)(2 * clusters)), kThreads, kSmemBytes, stream>>>(map_a, map_b, map_d, p);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }

@@ -14,6 +14,9 @@
 // memory-bound: the block scale (amax_b/6)/pts is first formed as one multiply and accepted only
 // when its E4M3 rounding provably equals that of the two true divisions (else those are done),
 // and (1/pts)/scale comes from a 128-entry table built per CTA with true divisions.
+#include <cstddef>
+#include <mutex>
+
 #include "common.cuh"
 #include "nvfp4_b200.h"
 
@@ -100,6 +103,13 @@ __device__ __forceinline__ void mul2(float a, float b, float s, float& d0, float
   asm("{.reg .b64 p, q, r; mov.b64 p, {%2, %3}; mov.b64 q, {%4, %4}; mul.rn.f32x2 r, p, q; mov.b64 {%0, %1}, r;}"
       : "=f"(d0), "=f"(d1) : "f"(a), "f"(b), "f"(s));
 }
+// (a, b) * s + 0: the product with an exact zero made +0 (-0 * s = -0, and -0 + +0 = +0), everything
+// else unchanged -- what the reference's matmul with H leaves, whose accumulator starts at +0
+__device__ __forceinline__ void mul2_poszero(float a, float b, float s, float& d0, float& d1) {
+  asm("{.reg .b64 p, q, r, z; mov.b64 p, {%2, %3}; mov.b64 q, {%4, %4}; mov.b64 z, {%5, %5};"
+      " fma.rn.f32x2 r, p, q, z; mov.b64 {%0, %1}, r;}"
+      : "=f"(d0), "=f"(d1) : "f"(a), "f"(b), "f"(s), "f"(0.0f));
+}
 // (a0, a1) and (b0, b1) -> sums into a, differences into b
 __device__ __forceinline__ void addsub2(float& a0, float& a1, float& b0, float& b1) {
   float s0, s1, d0, d1;
@@ -136,7 +146,8 @@ __device__ __forceinline__ Philox4 philox_rounds(uint32_t c0, uint32_t c1, uint3
 // 16 bf16 (8 words) -> fp32 v[16].  RHT: signs are applied by flipping sign bits of the packed
 // words, then the 16-point butterfly runs (strides 1, 2, 4, 8; the last three two lanes at a time);
 // the result is 4x the Hadamard transform (the 1/4 is folded into the scale by the caller).
-// A -0 can only leave the butterfly when all 16 inputs are zeros, which the caller handles.
+// An exact zero can leave the butterfly as -0 (a - b with a = -0, b = +0: a zero input under a
+// negative sign beside a subtree that cancels); the caller's scaling turns every exact zero into +0.
 template <bool RHT>
 __device__ __forceinline__ void expand(const uint32_t (&w)[8], const uint32_t (&sm)[8], float (&v)[16]) {
   if constexpr (!RHT) {
@@ -361,7 +372,10 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     const float recip = RHT ? recip_tab[sf] * 0.25f : recip_tab[sf];
     float d[16];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) mul2(v[2 * j], v[2 * j + 1], recip, d[2 * j], d[2 * j + 1]);
+    for (int j = 0; j < 8; ++j) {
+      if (RHT) mul2_poszero(v[2 * j], v[2 * j + 1], recip, d[2 * j], d[2 * j + 1]);
+      else mul2(v[2 * j], v[2 * j + 1], recip, d[2 * j], d[2 * j + 1]);
+    }
     uint32_t lo, hi;
     if (SR) {
       const Philox4 r = philox_rounds(i, 0u, (uint32_t)offset, (uint32_t)(offset >> 32), keys);
@@ -371,7 +385,6 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
       lo = e2m1x8_rn(d);
       hi = e2m1x8_rn(d + 8);
     }
-    if (RHT && amax_b == 0.0f) { lo = 0u; hi = 0u; }     // an all-zero block is +0 everywhere
     const uint32_t r = fast_div(i, div_bpr);
     const uint32_t kb = i - r * blk_per_row;
     *reinterpret_cast<uint2*>(qdata + (size_t)i * 8) = make_uint2(lo, hi);
@@ -444,40 +457,74 @@ using namespace nvfp4::fused;
 
 extern "C" size_t nvfp4_quantize_fused_workspace_bytes(void) { return sizeof(Workspace); }
 
-// Launch of the cooperative kernel.  amax_in == nullptr: two phases with the caller's workspace;
-// otherwise one quantize pass with the given per-tensor maximum (workspace unused, may be null).
-static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
-                        const float* signs16, uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
-                        float* pts_out, void* workspace, const float* amax_in, cudaStream_t stream) {
-  static int sm_count[64] = {};
-  static bool attr_done[64] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
-  if (sm_count[dev] == 0 &&
-      cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-    return NVFP4_E_LAUNCH;
-  const bool sr = mode == NVFP4_ROUND_STOCHASTIC;
-  const bool known = amax_in != nullptr;
-  constexpr int kThreadsKnown = 512, kBatchKnown = 3;
+namespace {
+
+constexpr int kThreadsKnown = 512, kBatchKnown = 3;
+constexpr int kMaxDevices = 64;
+
+// Per-device launch facts, looked up once under a lock (the entry points may be called from several
+// host threads): SM count, the shared-memory attribute of every instantiation, and how many CTAs of
+// the two-phase kernel the device keeps resident (its grid barrier needs all of them at once).
+struct DeviceInfo {
+  bool ready = false;
+  int sm_count = 0;
+  int coop_ctas = 0;          // resident CTAs of the two-phase kernel over the whole device
+};
+std::mutex g_info_mutex;
+DeviceInfo g_info[kMaxDevices];
+
+const void* fused_fn(bool sr, bool rht, bool known) {
 #define NVFP4_FUSED_FN(K_, T_, B_) \
   (sr ? (rht ? (const void*)quant_fused_kernel<true, true, K_, T_, B_> : (const void*)quant_fused_kernel<true, false, K_, T_, B_>) \
       : (rht ? (const void*)quant_fused_kernel<false, true, K_, T_, B_> : (const void*)quant_fused_kernel<false, false, K_, T_, B_>))
-  const void* fn = known ? NVFP4_FUSED_FN(true, kThreadsKnown, kBatchKnown) : NVFP4_FUSED_FN(false, kThreads, kBatch2);
+  return known ? NVFP4_FUSED_FN(true, kThreadsKnown, kBatchKnown) : NVFP4_FUSED_FN(false, kThreads, kBatch2);
 #undef NVFP4_FUSED_FN
-  if (!attr_done[dev]) {
-    const void* all[8] = {(const void*)quant_fused_kernel<true, true, false, kThreads, kBatch2>,
-                          (const void*)quant_fused_kernel<true, false, false, kThreads, kBatch2>,
-                          (const void*)quant_fused_kernel<false, true, false, kThreads, kBatch2>,
-                          (const void*)quant_fused_kernel<false, false, false, kThreads, kBatch2>,
-                          (const void*)quant_fused_kernel<true, true, true, kThreadsKnown, kBatchKnown>,
-                          (const void*)quant_fused_kernel<true, false, true, kThreadsKnown, kBatchKnown>,
-                          (const void*)quant_fused_kernel<false, true, true, kThreadsKnown, kBatchKnown>,
-                          (const void*)quant_fused_kernel<false, false, true, kThreadsKnown, kBatchKnown>};
-    for (const void* f : all)
-      if (cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-        return NVFP4_E_LAUNCH;
-    attr_done[dev] = true;
+}
+
+int device_info(DeviceInfo& out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return NVFP4_E_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_info_mutex);
+  DeviceInfo& d = g_info[dev];
+  if (!d.ready) {
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || d.sm_count < 1)
+      return NVFP4_E_LAUNCH;
+    for (int sr = 0; sr < 2; ++sr)
+      for (int rht = 0; rht < 2; ++rht)
+        for (int known = 0; known < 2; ++known)
+          if (cudaFuncSetAttribute(fused_fn(sr, rht, known), cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
+              cudaSuccess) {
+            cudaGetLastError();
+            return NVFP4_E_LAUNCH;
+          }
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fused_fn(true, true, false), kThreads, kSmemBytes) !=
+        cudaSuccess) {
+      cudaGetLastError();
+      return NVFP4_E_LAUNCH;
+    }
+    d.coop_ctas = per_sm * d.sm_count;
+    d.ready = true;
   }
+  out = d;
+  return NVFP4_OK;
+}
+
+}  // namespace
+
+// amax_in == nullptr: the two-phase kernel (cooperative launch: its grid barrier needs every CTA
+// resident) with the caller's workspace; otherwise one quantize pass with the given per-tensor
+// maximum, a plain launch with no barrier and no workspace (it may share the device with other work).
+static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
+                        const float* signs16, uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
+                        float* pts_out, void* workspace, const float* amax_in, cudaStream_t stream) {
+  DeviceInfo info;
+  const int irc = device_info(info);
+  if (irc != NVFP4_OK) return irc;
+  const bool sr = mode == NVFP4_ROUND_STOCHASTIC;
+  const bool known = amax_in != nullptr;
+  if (!known && info.coop_ctas < 1) return NVFP4_E_LAUNCH;
+  const void* fn = fused_fn(sr, rht != 0, known);
   const int64_t sm = (rows + 127) / 128 * 128, sk = (cols / 16 + 3) / 4 * 4;
   if (sm != rows || sk != cols / 16) {
     if (cudaMemsetAsync(scales, 0, (size_t)(sm * sk), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
@@ -485,7 +532,7 @@ static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, i
 
   uint32_t rows32 = (uint32_t)rows, bpr = (uint32_t)(cols / 16);
   const uint32_t total = rows32 * bpr;
-  uint32_t grid = (uint32_t)sm_count[dev];
+  uint32_t grid = (uint32_t)(known ? info.sm_count : (info.coop_ctas < info.sm_count ? info.coop_ctas : info.sm_count));
   const uint32_t min_per_cta = 2048;                       // do not spread tiny tensors over all SMs
   if ((uint64_t)grid * min_per_cta > total) grid = (total + min_per_cta - 1) / min_per_cta;
   if (grid < 1) grid = 1;
@@ -502,8 +549,13 @@ static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, i
   }
   void* args[] = {&xp, &rows32, &bpr, &ld, &fd, &signs16, &keys, &offset, &qdata, &scales, &pts_out, &ws, &per,
                   &contiguous, &amax_in};
-  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(known ? kThreadsKnown : kThreads), args, kSmemBytes, stream);
-  return e == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+  const cudaError_t e = known ? cudaLaunchKernel(fn, dim3(grid), dim3(kThreadsKnown), args, kSmemBytes, stream)
+                              : cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, kSmemBytes, stream);
+  if (e != cudaSuccess) {
+    cudaGetLastError();          // a refused launch must not show up as the next call's error
+    return NVFP4_E_LAUNCH;
+  }
+  return NVFP4_OK;
 }
 
 static int check_fused_args(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
@@ -532,8 +584,8 @@ extern "C" int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t co
 
 namespace nvfp4 { namespace fused {
 // For nvfp4_quantize_bf16 (row-wise output, maximum given): the same kernel as one streaming pass.
-// Returns NVFP4_E_LIMIT / NVFP4_E_ALIGN when this kernel does not take the case (the caller then
-// uses its plain kernel).
+// Returns NVFP4_E_LIMIT when this kernel does not take the case (the caller then uses its plain
+// kernel).
 int quantize_rows_known_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
                              const float* signs16, const float* amax, uint64_t seed, uint64_t offset,
                              uint8_t* qdata, uint8_t* scales, float* pts_out, cudaStream_t stream) {
@@ -560,33 +612,57 @@ static __device__ __align__(256) unsigned char g_static_scratch[256];
 // bound the single-launch kernel has); the scratch itself does not grow with the tensor.
 static constexpr long long kStaticMaxBlocks = (1ll << 31) - 1;
 
-#include <mutex>
 static std::mutex g_static_mutex;
-static void* g_static_ptr[64] = {};
+static void* g_static_ptr[kMaxDevices] = {};
+
+// Device address of the array on the current device.  The array's name is only a host-side handle
+// here, so the address has to be asked for (once per device, with that device current) before it
+// can be given to a kernel or a copy.
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return NVFP4_E_LAUNCH;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return NVFP4_E_LAUNCH;
+    }
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return NVFP4_OK;
+}
 
 extern "C" int nvfp4_quantize_static_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
                                           const float* signs16, uint64_t seed, uint64_t offset, uint8_t* qdata,
                                           uint8_t* scales, float* pts_out, void* stream_) {
   if (rows <= 0 || cols <= 0 || (cols & 15) != 0) return NVFP4_E_SHAPE;
   if (rows > kStaticMaxBlocks || (cols / 16) > kStaticMaxBlocks / rows) return NVFP4_E_LIMIT;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVFP4_E_LAUNCH;
   void* ptr = nullptr;
-  {
-    // Set-up, once per device, with that device current: the array's name is only a host-side
-    // handle here, so the device address has to be asked for before it can be given to a kernel.
-    std::lock_guard<std::mutex> lock(g_static_mutex);
-    if (g_static_ptr[dev] == nullptr) {
-      void* p = nullptr;
-      if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return NVFP4_E_LAUNCH;
-      g_static_ptr[dev] = p;
-    }
-    ptr = g_static_ptr[dev];
-  }
-  // The array keeps whatever the previous call (or an aborted one) left: the words the kernel
-  // expects to find zero are cleared on the stream first.  This is a memset, not an allocation.
-  if (cudaMemsetAsync(ptr, 0, sizeof(Workspace), static_cast<cudaStream_t>(stream_)) != cudaSuccess)
-    return NVFP4_E_LAUNCH;
+  const int rc = static_scratch_address(&ptr);
+  if (rc != NVFP4_OK) return rc;
+  // The array keeps whatever the previous call (or one that gave up) left.  The two barrier slots
+  // (the first 16 bytes) must start at zero and are cleared on the stream first; with both slots
+  // clean the launch counter may hold anything.  The error word behind them is NOT cleared: it stays
+  // set until nvfp4_quantize_static_status reads and clears it.  This is a memset, not an allocation.
+  if (cudaMemsetAsync(ptr, 0, 16, static_cast<cudaStream_t>(stream_)) != cudaSuccess) return NVFP4_E_LAUNCH;
   return nvfp4_quantize_fused_bf16(x, rows, cols, ld, mode, rht, signs16, seed, offset, qdata, scales, pts_out, ptr,
                                    sizeof(Workspace), stream_);
+}
+
+extern "C" int nvfp4_quantize_static_status(int32_t* host_out, int clear, void* stream_) {
+  if (host_out == nullptr) return NVFP4_E_NULL;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  void* ptr = nullptr;
+  const int rc = static_scratch_address(&ptr);
+  if (rc != NVFP4_OK) return rc;
+  unsigned char* word = static_cast<unsigned char*>(ptr) + offsetof(Workspace, error);
+  if (cudaMemcpyAsync(host_out, word, sizeof(int32_t), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      (clear && cudaMemsetAsync(word, 0, sizeof(int32_t), stream) != cudaSuccess) ||
+      cudaStreamSynchronize(stream) != cudaSuccess) {
+    cudaGetLastError();
+    return NVFP4_E_LAUNCH;
+  }
+  return NVFP4_OK;
 }

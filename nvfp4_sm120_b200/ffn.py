@@ -31,16 +31,15 @@ class SwiGLUFFN(nn.Module):
                 bound = 1.0 / math.sqrt(lin.weight.shape[1])          # kaiming_uniform_(a=sqrt(5))
                 lin.weight.uniform_(-bound, bound, generator=g)
 
-        # one sign vector serves the maxima of both gradient tensors in the fused backward
-        if self.fused and not (torch.equal(self.gate.signs, self.up.signs) and
-                               torch.equal(self.gate.signs, self.down.signs)):
-            self.fused = False
+        # One sign vector serves the Hadamard maxima the fused kernels compute; a consumer whose own
+        # vector differs (a checkpoint may change the buffers) recomputes that maximum, see
+        # FP4Linear.forward(amax_signs=) and linear.hint_grad_amax(signs=).
 
     def forward(self, x):
         g, u = self.gate(x), self.up(x)
         if self.fused and isinstance(self.down, FP4Linear) and g.dtype == torch.bfloat16 and g.is_cuda:
             h, h_max = swiglu(g, u, self.gate.signs if g.numel() // g.shape[-1] % 16 == 0 else None)
-            return self.down(h, amax=h_max)
+            return self.down(h, amax=h_max, amax_signs=self.gate.signs)
         return self.down(F.silu(g) * u)
 
 

@@ -21,6 +21,8 @@ def gemm_status(device=None) -> int:
     """Device status word of the GEMM kernels on `device`: 0, or the code of the first bounded
     wait that gave up.  Reading it synchronises."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
     return int(_status_word(device).item())
 
 
@@ -42,13 +44,14 @@ def nvfp4_mm(a: NVFP4Tensor, b: NVFP4Tensor, out_dtype=None, out=None) -> torch.
         out_dtype = torch.float32 if a.orig_dtype == torch.float32 else torch.bfloat16
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("out_dtype must be bfloat16 or float32")
-    dev = a.qdata.device
+    dev = _lib.cuda_device_of(a.qdata, a.scale, a.per_tensor_scale, b.qdata, b.scale, b.per_tensor_scale, out)
     d = out if out is not None else torch.empty((m, n), dtype=out_dtype, device=dev)
-    code = _lib.lib().nvfp4_gemm(
-        a.qdata.data_ptr(), a.scale.data_ptr(), a.per_tensor_scale.data_ptr(),
-        b.qdata.data_ptr(), b.scale.data_ptr(), b.per_tensor_scale.data_ptr(),
-        d.data_ptr(), _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16,
-        m, n, k2 * 2, d.stride(0), _status_word(dev).data_ptr(), _stream())
+    with torch.cuda.device(dev):                   # the C side launches on the current device
+        code = _lib.lib().nvfp4_gemm(
+            a.qdata.data_ptr(), a.scale.data_ptr(), a.per_tensor_scale.data_ptr(),
+            b.qdata.data_ptr(), b.scale.data_ptr(), b.per_tensor_scale.data_ptr(),
+            d.data_ptr(), _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16,
+            m, n, k2 * 2, d.stride(0), _status_word(dev).data_ptr(), _stream(dev))
     _lib.check(code, "nvfp4_gemm")
     return d
 

@@ -38,20 +38,52 @@ def mark_step():
 # Maxima of gradient tensors that a fused producer already knows (swiglu.SwiGLUFn.backward): keyed by
 # the address of the gradient, which the entry keeps alive so that the address cannot be reused while
 # the hint exists.  FP4LinearFn.backward takes the hint of the gradient it is handed and then skips
-# its amax passes.  Entries that are never taken are dropped by mark_step().
+# its amax passes.  Entries that are never taken are dropped by mark_step(), and the table never
+# holds more than _GRAD_AMAX_MAX of them (oldest dropped first), so a caller that never calls
+# mark_step() does not keep gradients alive without bound.
 _GRAD_AMAX = {}
+_GRAD_AMAX_MAX = 64
 
 
-def hint_grad_amax(grad, maxima2, has_rht):
-    """maxima2: fp32 [2] on the device = max|grad| and max|RHT_tokens(grad)| (valid if has_rht)."""
-    _GRAD_AMAX[grad.data_ptr()] = (grad, maxima2, bool(has_rht))
+_SIGNS_EQ = {}
 
 
-def _take_grad_amax(gy2):
+def _signs_key(signs):
+    """Identity of a sign vector as the kernels saw it: its storage address and version counter."""
+    return None if signs is None else (signs.data_ptr(), signs._version)
+
+
+def _same_signs(a, b):
+    """Do two sign vectors hold the same 16 values?  Compared once per pair of (address, version) --
+    the comparison reads the device -- and remembered, so the hot path never synchronises."""
+    if a is None or b is None:
+        return a is b
+    ka, kb = _signs_key(a), _signs_key(b)
+    if ka == kb:
+        return True
+    key = (ka, kb)
+    if key not in _SIGNS_EQ:
+        if len(_SIGNS_EQ) > 256:
+            _SIGNS_EQ.clear()
+        _SIGNS_EQ[key] = bool(a.device == b.device and a.shape == b.shape and torch.equal(a, b))
+    return _SIGNS_EQ[key]
+
+
+def hint_grad_amax(grad, maxima2, has_rht, signs=None):
+    """maxima2: fp32 [2] on the device = max|grad| and max|RHT_tokens(grad)|.  The second is valid if
+    has_rht and was computed with the sign vector `signs`; a consumer with another sign vector
+    recomputes it."""
+    while len(_GRAD_AMAX) >= _GRAD_AMAX_MAX:
+        _GRAD_AMAX.pop(next(iter(_GRAD_AMAX)))
+    _GRAD_AMAX[grad.data_ptr()] = (grad, maxima2, bool(has_rht), signs, None if signs is None else signs._version)
+
+
+def _take_grad_amax(gy2, signs=None):
     e = _GRAD_AMAX.pop(gy2.data_ptr(), None)
     if e is None or e[0].numel() != gy2.numel() or e[0].dtype != gy2.dtype or e[0].shape[-1] != gy2.shape[-1]:
         return None, None
-    return e[1][0:1], (e[1][1:2] if e[2] else None)
+    rht_ok = e[2] and (e[3] is None or (e[3]._version == e[4] and _same_signs(e[3], signs)))
+    return e[1][0:1], (e[1][1:2] if rht_ok else None)
 
 
 def set_amortize(flag: bool):
@@ -70,7 +102,8 @@ class FP4LinearFn(torch.autograd.Function):
     word of a tensor that is sharded across ranks before it is used (tensor parallelism)."""
 
     @staticmethod
-    def forward(ctx, x, w, H, signs, wq_K, wq_N, amax_reduce=None, sharded=(False, False), x_amax=None):   # callers pass all nine
+    def forward(ctx, x, w, H, signs, wq_K, wq_N, amax_reduce=None, sharded=(False, False), x_amax=None,
+                x_amax_rht=True):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         x_sharded, y_sharded = sharded                 # is the K dim / the N dim split across ranks?
@@ -85,6 +118,7 @@ class FP4LinearFn(torch.autograd.Function):
         ctx.save_for_backward(x2, w)
         ctx.H, ctx.signs, ctx.xshape, ctx.wq_N = H, signs, x.shape, wq_N
         ctx.amax_reduce, ctx.sharded, ctx.x_amax = amax_reduce, sharded, x_amax
+        ctx.x_amax_rht = bool(x_amax_rht)        # False: the Hadamard maximum came from another sign vector
         return y.reshape(*x.shape[:-1], w.shape[0]).to(x.dtype)
 
     @staticmethod
@@ -93,8 +127,8 @@ class FP4LinearFn(torch.autograd.Function):
         H, signs, wq_N, red = ctx.H, ctx.signs, ctx.wq_N, ctx.amax_reduce
         x_sharded, y_sharded = ctx.sharded
         gy2 = gy.reshape(-1, w.shape[0])
-        g_amax, g_amax_rht = _take_grad_amax(gy2)      # known to a fused producer of gy, else None
-        x_amax_rht = None if ctx.x_amax is None else ctx.x_amax[1:2]
+        g_amax, g_amax_rht = _take_grad_amax(gy2, signs)      # known to a fused producer of gy, else None
+        x_amax_rht = None if (ctx.x_amax is None or not ctx.x_amax_rht) else ctx.x_amax[1:2]
         dx = dw = None
         if ctx.needs_input_grad[0]:
             # dgrad: dX = dY @ W, contraction over N; dY gets stochastic rounding
@@ -109,7 +143,7 @@ class FP4LinearFn(torch.autograd.Function):
             xtq = _quant(x2, red if x_sharded else None, rht=True, H=H, signs=signs, transpose=True,
                          amax=x_amax_rht)
             dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
-        return dx, dw, None, None, None, None, None, None, None
+        return dx, dw, None, None, None, None, None, None, None, None
 
 
 def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False, amax=None):
@@ -170,12 +204,15 @@ class FP4Linear(nn.Module):
     def _wq_N(self):
         return self._cache.wq_N
 
-    def forward(self, x, amax=None):
-        """amax: optional fp32 [2] from a fused producer of x (see FP4LinearFn.forward)."""
+    def forward(self, x, amax=None, amax_signs=None):
+        """amax: optional fp32 [2] from a fused producer of x (see FP4LinearFn.forward); amax_signs: the
+        sign vector its Hadamard maximum was computed with (None = this layer's own).  When it is not
+        this layer's vector, only the plain maximum is used and the other is recomputed."""
         if x.is_cuda and torch.is_autocast_enabled("cuda"):
             x = x.to(torch.get_autocast_dtype("cuda"))       # what autocast does for nn.Linear
         wq_K, wq_N = self._cache.get(self.weight)
-        return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, None, (False, False), amax)
+        rht_ok = amax_signs is None or _same_signs(amax_signs, self.signs)
+        return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, None, (False, False), amax, rht_ok)
 
     def extra_repr(self):
         return f"in_features={self.weight.shape[1]}, out_features={self.weight.shape[0]}, bias=False, nvfp4"

@@ -57,9 +57,10 @@ class DecoderBlock(nn.Module):
         self.o = make_linear(dim, dim, use_fp4, device)
         self.up = make_linear(dim, hidden, use_fp4, device)
         self.down = make_linear(hidden, dim, use_fp4, device)
-        # the fused activation computes the Hadamard maxima for `down` and for `up`'s gradient with one
-        # sign vector: both linears must hold the same one (they do unless a checkpoint changed them)
-        self.fused_act = bool(use_fp4 and torch.equal(self.up.signs, self.down.signs))
+        # the fused activation computes the Hadamard maxima for `down` and for `up`'s gradient with
+        # `down`'s sign vector; a consumer holding another vector recomputes its maximum (checked at
+        # call time: a checkpoint may change the buffers)
+        self.fused_act = bool(use_fp4)
 
     def forward(self, x, cos, sin):
         B, T, _ = x.shape
@@ -77,7 +78,7 @@ class DecoderBlock(nn.Module):
                 and u.shape[-1] % 8 == 0):
             # fused relu^2 that also hands `down` the maxima of its input (and `up` those of its gradient)
             a, a_max = relu2(u, self.down.signs if (B * T) % 16 == 0 else None)
-            return x + self.down(a, amax=a_max)
+            return x + self.down(a, amax=a_max, amax_signs=self.down.signs)
         return x + self.down(F.relu(u).square())
 
 

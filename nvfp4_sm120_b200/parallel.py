@@ -102,14 +102,17 @@ class _ParallelLinearBase(nn.Module):
             self._cache = None
             self.H = self.signs = None
 
-    def _call(self, x, sharded, x_amax=None):
-        """x_amax: this rank's maxima of x from a fused producer (swiglu.SwiGLUFn), FP4 path only."""
+    def _call(self, x, sharded, x_amax=None, x_amax_signs=None):
+        """x_amax: this rank's maxima of x from a fused producer (swiglu.SwiGLUFn), FP4 path only;
+        x_amax_signs: the sign vector its Hadamard maximum was computed with."""
         wq_K = wq_N = None
         if self._cache is not None:
             wq_K, wq_N = self._cache.get(self.weight, self.amax_reduce)
         if x_amax is not None and self.linear_fn is _fp4_linear_fn:
-            from .linear import FP4LinearFn
-            return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, self.amax_reduce, sharded, x_amax)
+            from .linear import FP4LinearFn, _same_signs
+            rht_ok = x_amax_signs is None or _same_signs(x_amax_signs, self.signs)
+            return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, self.amax_reduce, sharded, x_amax,
+                                     rht_ok)
         return self.linear_fn(x, self.weight, self.H, self.signs, wq_K, wq_N, self.amax_reduce, sharded)
 
 
@@ -126,8 +129,8 @@ class RowParallelFP4Linear(_ParallelLinearBase):
     """y[*, out] = sum over ranks of x_local @ W_local^T.  The input is split along the feature dim
     (its amax is reduced); the output is summed over the group and is then replicated."""
 
-    def forward(self, x_local, amax=None):
-        y = self._call(x_local, (True, False), amax)
+    def forward(self, x_local, amax=None, amax_signs=None):
+        y = self._call(x_local, (True, False), amax, amax_signs)
         return _ReduceFromGroup.apply(y, self.group)
 
 
@@ -156,7 +159,7 @@ class TensorParallelSwiGLU(nn.Module):
             from .swiglu import swiglu
             tokens = g.numel() // g.shape[-1]
             h, h_max = swiglu(g, u, self.gate.signs if tokens % 16 == 0 else None)
-            return self.down(h, amax=h_max)
+            return self.down(h, amax=h_max, amax_signs=self.gate.signs)
         return self.down(F.silu(g) * u)
 
 

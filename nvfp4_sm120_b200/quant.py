@@ -54,7 +54,7 @@ _WS = {}
 def _workspace(device):
     """64-byte scratch of the single-launch quantizer, zeroed once, one per (device, stream): every
     launch leaves it ready for the next, and launches on one stream never overlap."""
-    key = (device, torch.cuda.current_stream().cuda_stream)
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
     if key not in _WS:
         _WS[key] = torch.zeros(16, dtype=torch.int32, device=device)
     return _WS[key]
@@ -64,12 +64,15 @@ def fused_error(device=None) -> int:
     """Sticky error word of the single-launch quantizer's workspace on the current stream
     (0 = none).  Reading it synchronises."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    key = (device, torch.cuda.current_stream().cuda_stream)
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
     return int(_WS[key][4].item()) if key in _WS else 0
 
 
-def _stream():
-    return torch.cuda.current_stream().cuda_stream
+def _stream(device=None):
+    """Handle of torch's current stream on `device` (default: the current device)."""
+    return torch.cuda.current_stream(device).cuda_stream
 
 
 def _as_bf16_rows(t):
@@ -89,9 +92,11 @@ def tensor_amax(t, rht=False, signs=None, transpose=False, out=None):
     x = _as_bf16_rows(t)
     amax = out if out is not None else torch.empty(1, device=x.device, dtype=torch.float32)
     sg = _signs(signs, x.device) if rht else None
-    code = _lib.lib().nvfp4_amax_bf16(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), int(rht),
-                                      int(transpose), sg.data_ptr() if rht else None,
-                                      amax.data_ptr(), 1, _stream())
+    dev = _lib.cuda_device_of(x, amax, sg)
+    with torch.cuda.device(dev):                   # the C side launches on the current device
+        code = _lib.lib().nvfp4_amax_bf16(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), int(rht),
+                                          int(transpose), sg.data_ptr() if rht else None,
+                                          amax.data_ptr(), 1, _stream(dev))
     _lib.check(code, "nvfp4_amax_bf16")
     return amax
 
@@ -123,22 +128,25 @@ def quant_nvfp4(t, stochastic=False, rht=False, H=None, signs=None, seed=None, *
     qdata = torch.empty((m, k // 2), dtype=torch.uint8, device=dev)
     scale = torch.empty((sm, sk), dtype=torch.uint8, device=dev)
     pts = torch.empty((), dtype=torch.float32, device=dev)
+    _lib.cuda_device_of(x, sg, amax)
     if fused and amax is None and not transpose and rows * (cols // BLK) < 2 ** 31:
-        ws = _workspace(dev)
-        code = _lib.lib().nvfp4_quantize_fused_bf16(
-            x.data_ptr(), rows, cols, x.stride(0),
-            _lib.ROUND_STOCHASTIC if stochastic else _lib.ROUND_NEAREST, int(rht),
-            sg.data_ptr() if rht else None, int(seed) & (2 ** 64 - 1), int(philox_offset),
-            qdata.data_ptr(), scale.data_ptr(), pts.data_ptr(), ws.data_ptr(), 64, _stream())
+        with torch.cuda.device(dev):               # the C side launches on the current device
+            ws = _workspace(dev)
+            code = _lib.lib().nvfp4_quantize_fused_bf16(
+                x.data_ptr(), rows, cols, x.stride(0),
+                _lib.ROUND_STOCHASTIC if stochastic else _lib.ROUND_NEAREST, int(rht),
+                sg.data_ptr() if rht else None, int(seed) & (2 ** 64 - 1), int(philox_offset),
+                qdata.data_ptr(), scale.data_ptr(), pts.data_ptr(), ws.data_ptr(), 64, _stream(dev))
         _lib.check(code, "nvfp4_quantize_fused_bf16")
         return NVFP4Tensor(qdata, scale.view(torch.float8_e4m3fn), BLK, t.dtype, pts, True)
     if amax is None:
         amax = tensor_amax(x, rht, sg, transpose)
-    code = _lib.lib().nvfp4_quantize_bf16(
-        x.data_ptr(), rows, cols, x.stride(0), int(transpose),
-        _lib.ROUND_STOCHASTIC if stochastic else _lib.ROUND_NEAREST, int(rht),
-        sg.data_ptr() if rht else None, amax.data_ptr(), int(seed) & (2 ** 64 - 1), int(philox_offset),
-        qdata.data_ptr(), scale.data_ptr(), pts.data_ptr(), _stream())
+    with torch.cuda.device(dev):
+        code = _lib.lib().nvfp4_quantize_bf16(
+            x.data_ptr(), rows, cols, x.stride(0), int(transpose),
+            _lib.ROUND_STOCHASTIC if stochastic else _lib.ROUND_NEAREST, int(rht),
+            sg.data_ptr() if rht else None, amax.data_ptr(), int(seed) & (2 ** 64 - 1), int(philox_offset),
+            qdata.data_ptr(), scale.data_ptr(), pts.data_ptr(), _stream(dev))
     _lib.check(code, "nvfp4_quantize_bf16")
     return NVFP4Tensor(qdata, scale.view(torch.float8_e4m3fn), BLK, t.dtype, pts, True)
 

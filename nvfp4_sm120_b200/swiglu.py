@@ -31,12 +31,13 @@ class SwiGLUFn(torch.autograd.Function):
         sg = _signs(signs, g.device) if use_rht else None
         h = torch.empty_like(g2)
         maxima = torch.empty(2, dtype=torch.float32, device=g.device)
-        code = _lib.lib().nvfp4_swiglu_fwd_bf16(g2.data_ptr(), u2.data_ptr(), rows, cols, g2.stride(0), h.data_ptr(),
-                                                h.stride(0), sg.data_ptr() if use_rht else None, maxima.data_ptr(),
-                                                1, _stream())
+        with torch.cuda.device(g2.device):           # the C side launches on the current device
+            code = _lib.lib().nvfp4_swiglu_fwd_bf16(g2.data_ptr(), u2.data_ptr(), rows, cols, g2.stride(0), h.data_ptr(),
+                                                    h.stride(0), sg.data_ptr() if use_rht else None, maxima.data_ptr(),
+                                                    1, _stream(g2.device))
         _lib.check(code, "nvfp4_swiglu_fwd_bf16")
         ctx.save_for_backward(g2, u2)
-        ctx.sg, ctx.use_rht, ctx.shape = sg, use_rht, g.shape
+        ctx.sg, ctx.use_rht, ctx.shape, ctx.signs_in = sg, use_rht, g.shape, signs
         ctx.mark_non_differentiable(maxima)
         return h.reshape(g.shape), maxima
 
@@ -50,15 +51,16 @@ class SwiGLUFn(torch.autograd.Function):
         rows, cols = g2.shape
         dg, du = torch.empty_like(g2), torch.empty_like(g2)
         maxima = torch.empty(4, dtype=torch.float32, device=g2.device)
-        code = _lib.lib().nvfp4_swiglu_bwd_bf16(g2.data_ptr(), u2.data_ptr(), d2.data_ptr(), rows, cols, g2.stride(0),
-                                                dg.data_ptr(), du.data_ptr(), dg.stride(0),
-                                                ctx.sg.data_ptr() if ctx.use_rht else None, maxima.data_ptr(), 1,
-                                                _stream())
+        with torch.cuda.device(g2.device):           # the C side launches on the current device
+            code = _lib.lib().nvfp4_swiglu_bwd_bf16(g2.data_ptr(), u2.data_ptr(), d2.data_ptr(), rows, cols, g2.stride(0),
+                                                    dg.data_ptr(), du.data_ptr(), dg.stride(0),
+                                                    ctx.sg.data_ptr() if ctx.use_rht else None, maxima.data_ptr(), 1,
+                                                    _stream(g2.device))
         _lib.check(code, "nvfp4_swiglu_bwd_bf16")
         dg, du = dg.reshape(ctx.shape), du.reshape(ctx.shape)
         # the linears that produced g and u will quantize exactly these tensors in their backward
-        _linear.hint_grad_amax(dg, maxima[0:2], ctx.use_rht)
-        _linear.hint_grad_amax(du, maxima[2:4], ctx.use_rht)
+        _linear.hint_grad_amax(dg, maxima[0:2], ctx.use_rht, ctx.signs_in)
+        _linear.hint_grad_amax(du, maxima[2:4], ctx.use_rht, ctx.signs_in)
         return dg, du, None
 
 
@@ -82,11 +84,12 @@ class ReLU2Fn(torch.autograd.Function):
         sg = _signs(signs, x.device) if use_rht else None
         out = torch.empty_like(x2)
         maxima = torch.empty(2, dtype=torch.float32, device=x.device)
-        code = _lib.lib().nvfp4_relu2_fwd_bf16(x2.data_ptr(), rows, cols, x2.stride(0), out.data_ptr(), out.stride(0),
-                                               sg.data_ptr() if use_rht else None, maxima.data_ptr(), 1, _stream())
+        with torch.cuda.device(x2.device):           # the C side launches on the current device
+            code = _lib.lib().nvfp4_relu2_fwd_bf16(x2.data_ptr(), rows, cols, x2.stride(0), out.data_ptr(), out.stride(0),
+                                                   sg.data_ptr() if use_rht else None, maxima.data_ptr(), 1, _stream(x2.device))
         _lib.check(code, "nvfp4_relu2_fwd_bf16")
         ctx.save_for_backward(x2)
-        ctx.sg, ctx.use_rht, ctx.shape = sg, use_rht, x.shape
+        ctx.sg, ctx.use_rht, ctx.shape, ctx.signs_in = sg, use_rht, x.shape, signs
         ctx.mark_non_differentiable(maxima)
         return out.reshape(x.shape), maxima
 
@@ -100,12 +103,13 @@ class ReLU2Fn(torch.autograd.Function):
         rows, cols = x2.shape
         dx = torch.empty_like(x2)
         maxima = torch.empty(2, dtype=torch.float32, device=x2.device)
-        code = _lib.lib().nvfp4_relu2_bwd_bf16(x2.data_ptr(), d2.data_ptr(), rows, cols, x2.stride(0), dx.data_ptr(),
-                                               dx.stride(0), ctx.sg.data_ptr() if ctx.use_rht else None,
-                                               maxima.data_ptr(), 1, _stream())
+        with torch.cuda.device(x2.device):           # the C side launches on the current device
+            code = _lib.lib().nvfp4_relu2_bwd_bf16(x2.data_ptr(), d2.data_ptr(), rows, cols, x2.stride(0), dx.data_ptr(),
+                                                   dx.stride(0), ctx.sg.data_ptr() if ctx.use_rht else None,
+                                                   maxima.data_ptr(), 1, _stream(x2.device))
         _lib.check(code, "nvfp4_relu2_bwd_bf16")
         dx = dx.reshape(ctx.shape)
-        _linear.hint_grad_amax(dx, maxima, ctx.use_rht)
+        _linear.hint_grad_amax(dx, maxima, ctx.use_rht, ctx.signs_in)
         return dx, None
 
 
