@@ -32,6 +32,26 @@ BYTES_PER_MODE = ROWS * COLS * 2 + ROWS * COLS // 2 + ROWS * COLS // 16      # 8
 MODES = ("rne", "sr", "rht_sr")
 N_BUF = 6                                   # 6 x 64 MiB inputs = 384 MiB, three times the 126 MB L2
 SR_SEED, SIGN_SEED, DATA_SEED = 7, 3, 1
+METRIC = "quantizer HBM GB/s @8192x4096"
+# one description of the workload for both arms (the GPU arm and --impl reference)
+CONFIG = {"workload": "quantizer sweep bf16 8192x4096: RNE, SR (Philox seed 7), RHT (sign seed 3)+SR",
+          "bytes_per_mode": BYTES_PER_MODE, "modes_per_step": 3,
+          "l2": f"GPU arm: inputs rotate over {N_BUF} tensors of 64 MiB (384 MiB, larger than the 126 MB L2); "
+                "reference arm: host run",
+          "launch": "GPU arm: one CUDA graph per input tensor, replayed", "multi_gpu": "replicas only"}
+
+
+def measured_traffic():
+    """DRAM read + write bytes per launch of the single-launch quantizer from the tracked ncu summary
+    of the same kernel and size (a line `traffic_bytes_per_launch: N`), or None when it is absent."""
+    import re
+    p = os.path.join(ROOT, "profiles", "quant_fused_8192x4096.md")
+    try:
+        with open(p) as f:
+            m = re.search(r"traffic_bytes_per_launch:\s*([0-9.eE+]+)", f.read())
+        return float(m.group(1)) if m else None
+    except OSError:
+        return None
 
 
 def measured_peaks():
@@ -146,11 +166,10 @@ def run_reference_arm(args, rank, world):
     gbs = 3 * (rows * COLS * (2 + 0.5 + 1 / 16)) / dt / 1e9
     sample = f"{rows} of {ROWS} rows x {COLS} cols per step, three modes (RNE, SR, RHT+SR)"
     line = {
-        "impl": "reference", "metric": "quantizer HBM GB/s @8192x4096", "value": gbs, "unit": "GB/s",
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "quantizer sweep bf16 8192x4096: RNE, SR (Philox seed 7), RHT (sign seed 3)+SR",
-                   "l2": "host run"},
+        "config": CONFIG,
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -179,7 +198,10 @@ def run_gpu_arm(args, rank, world, local_rank):
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a rank that fails inside an extra must not leave the others waiting for the default 10 minutes
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=datetime.timedelta(seconds=240))
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     lib = _lib.lib()
@@ -359,13 +381,10 @@ def run_gpu_arm(args, rank, world, local_rank):
     d2h = 3 * (ROWS * COLS // 2 + sm * sk + 4)
 
     line = {
-        "metric": "quantizer HBM GB/s @8192x4096", "value": value, "unit": "GB/s", "n_gpus": world,
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "quantizer sweep bf16 8192x4096: RNE, SR (Philox seed 7), RHT (sign seed 3)+SR",
-                   "bytes_per_mode": BYTES_PER_MODE, "modes_per_step": 3,
-                   "l2": f"inputs rotate over {N_BUF} tensors of 64 MiB (384 MiB, larger than the 126 MB L2)",
-                   "launch": "one CUDA graph per input tensor, replayed", "multi_gpu": "replicas only"},
+        "config": CONFIG,
         "clocks": clocks,
         "gpu_launches": 3 * args.steps,
         "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -374,9 +393,9 @@ def run_gpu_arm(args, rank, world, local_rank):
                         "over three streams so that copy-in, kernels and copy-out of neighbouring steps overlap; "
                         "timed from before the first copy-in to after the last copy-out"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": achieved / hbm_peak, "traffic": 69.7e6, "peak_kind": peak_kind,
-                     "traffic_note": "dram read+write bytes per launch, ncu capture of the same kernel and size "
-                                     "(profiles/quant_fused_8192x4096.md)",
+                     "frac": achieved / hbm_peak, "traffic": measured_traffic(), "peak_kind": peak_kind,
+                     "traffic_note": "dram read + write bytes per launch from an ncu capture of the same kernel and "
+                                     "size (the tracked summary of that capture), mean of the three modes",
                      "kernel": "quant_fused_kernel, one launch per mode (algorithmic bytes of the three modes / summed event time)"},
         "modes": kern,
         "quantizer_error_word": quant_mod.fused_error(dev),
@@ -403,18 +422,66 @@ def run_gpu_arm(args, rank, world, local_rank):
                 line["extras"] = extras(Q, dev, bf16_peak, peak_kind)
             except Exception as exc:
                 line["extras"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+            try:
+                line["extras"]["dp_gpt124m"] = extras_data_parallel(Q, dev, 0, 1, None)
+            except Exception as exc:
+                line["extras"]["dp_gpt124m"] = {"error": f"{type(exc).__name__}: {exc}"[:300]}
     if world > 1 and not args.no_extras:
         try:
             tp = extras_tensor_parallel(Q, dev, rank, world, dist)
         except Exception as exc:
             tp = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        try:
+            dp = extras_data_parallel(Q, dev, rank, world, dist, backends=("fp4",))
+        except Exception as exc:
+            dp = {"error": f"{type(exc).__name__}: {exc}"[:300]}
         if rank == 0:
-            line["extras"] = {"ffn_tensor_parallel": tp}
+            line["extras"] = {"ffn_tensor_parallel": tp, "dp_gpt124m": dp}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def extras_data_parallel(Q, dev, rank, world, dist, backends=("fp4", "bf16")):
+    """benchmark config 5 on `world` GPUs: GPT 12 layers / d 768 / 12 heads / MLP 4x / vocab 50257,
+    seq 1024, 256 sequences per optimizer step split over the ranks (strong scaling), every linear of
+    every block an FP4Linear, AdamW, synthetic Zipf(1.1) token ids; bf16 gradient all-reduce over NCCL
+    overlapped with the last backward pass.  One warm-up step, two timed steps, device time, max over
+    ranks; tokens/s = 262 144 tokens / step time."""
+    from nvfp4_sm120_b200.train import Trainer
+    res = {}
+    for backend in backends:
+        tr = Trainer(dev, rank, world, backend=backend, all_fp4=True, total_steps=300)
+        tr.step(20)                                   # warm-up at a mid-schedule learning rate
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        n = 2
+        for i in range(n):
+            loss = tr.step(21 + i)
+        e1.record()
+        e1.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        res[backend] = {"ms_per_step": ms, "tokens_per_s": tr.global_batch * tr.seq / (ms * 1e-3),
+                        "loss_after_3_steps": float(loss), "fp4_linears": len(tr.model.fp4_linears()),
+                        "microbatches_per_rank": tr.accum}
+        if tr.reducer is not None:
+            res[backend]["gradient_buckets"] = len(tr.reducer.buckets)
+            tr.reducer.remove()
+        del tr
+        torch.cuda.empty_cache()
+    Q.set_amortize(False)
+    res["config"] = ("GPT-124M, 256 x 1024 tokens per step over all ranks, all 72 block linears FP4, AdamW, bf16 "
+                     "gradient all-reduce overlapped with backward; scaling: strong")
+    res["dp"] = world
+    return res
 
 
 def extras_tensor_parallel(Q, dev, rank, world, dist):
@@ -487,10 +554,49 @@ def extras_tensor_parallel(Q, dev, rank, world, dist):
             "config": "SwiGLU d4096 h14336, 8 microbatches x 4096 tokens, fwd+bwd, TP over NCCL"}
 
 
+def library_fp4_mm(qa, qb):
+    """The library comparator, bench-side only: cuBLASLt's block-scaled NVFP4 GEMM reached through
+    torch's scaled matmul on the SAME quantized operands (what the reference's fp4_matmul dispatches
+    to through torchao, nvfp4_gemm.py:57).  Returns (callable(out) or None, description)."""
+    import torch.nn.functional as F
+    a4 = qa.qdata.view(torch.float4_e2m1fn_x2)
+    b4 = qb.qdata.view(torch.float4_e2m1fn_x2).t()
+    sa, sb = qa.scale.reshape(-1), qb.scale.reshape(-1)
+    ga, gb = qa.per_tensor_scale.reshape(1), qb.per_tensor_scale.reshape(1)
+    tried = []
+    if hasattr(F, "scaled_mm") and hasattr(F, "ScalingType"):
+        ST, SW = F.ScalingType, F.SwizzleType
+        def two_level():
+            return F.scaled_mm(a4, b4, [sa, ga], [ST.BlockWise1x16, ST.TensorWise], [sb, gb],
+                               [ST.BlockWise1x16, ST.TensorWise], [SW.SWIZZLE_32_4_4, SW.NO_SWIZZLE],
+                               [SW.SWIZZLE_32_4_4, SW.NO_SWIZZLE], output_dtype=torch.bfloat16)
+        def one_level():
+            return F.scaled_mm(a4, b4, sa, ST.BlockWise1x16, sb, ST.BlockWise1x16, SW.SWIZZLE_32_4_4,
+                               SW.SWIZZLE_32_4_4, output_dtype=torch.bfloat16)
+        for name, fn in (("F.scaled_mm block 1x16 + per-tensor scale", two_level),
+                         ("F.scaled_mm block 1x16 scales only (per-tensor scales left out of the timed call)", one_level)):
+            try:
+                fn()
+                torch.cuda.synchronize()
+                return fn, name
+            except Exception as exc:                 # try the next spelling
+                tried.append(f"{name}: {type(exc).__name__}: {str(exc)[:80]}")
+    try:
+        fn = lambda: torch._scaled_mm(a4, b4, sa, sb, out_dtype=torch.bfloat16)
+        fn()
+        torch.cuda.synchronize()
+        return fn, "torch._scaled_mm block scales only (per-tensor scales left out of the timed call)"
+    except Exception as exc:
+        tried.append(f"torch._scaled_mm: {type(exc).__name__}: {str(exc)[:80]}")
+    return None, "unavailable: " + " | ".join(tried)
+
+
 def extras(Q, dev, bf16_peak, peak_kind):
-    """Beside the headline: FP4 GEMM throughput on benchmark config 3 shapes with bf16 torch.matmul
-    alongside, and the SwiGLU FFN of config 4 (d 4096, h 14336, 8 x 4096 tokens) forward+backward in
-    FP4 (amortized weight quantization) against the same block in bf16."""
+    """Beside the headline: FP4 GEMM throughput on benchmark config 3 shapes with the library's FP4
+    GEMM (cuBLASLt through torch, same quantized operands) and bf16 torch.matmul alongside, each as a
+    burst figure (single launches, L2 flushed, after a pause) and a sustained one (back to back for
+    about a second); then the SwiGLU FFN of config 4 (d 4096, h 14336, 8 x 4096 tokens)
+    forward+backward in FP4 (amortized weight quantization) against the same block in bf16."""
     out = {"gemm": []}
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     for (m, n, k) in [(4096, 4096, 4096), (8192, 8192, 8192), (16384, 16384, 16384), (16384, 4096, 14336)]:
@@ -499,31 +605,46 @@ def extras(Q, dev, bf16_peak, peak_kind):
         Bt = torch.randn(n, k, device=dev, dtype=torch.bfloat16, generator=g)
         qa, qb = Q.quant_nvfp4(A), Q.quant_nvfp4(Bt)
         d = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
-
-        def fp4(_):
-            Q.nvfp4_mm(qa, qb.t(), out=d)
-
-        def bf16(_):
-            torch.matmul(A, Bt.t(), out=d)
-        res = {}
-        for name, fn in (("fp4", fp4), ("bf16", bf16)):
-            # single launches are burst numbers: let the previous shape's seconds of dense GEMMs drain
-            # out of the power/thermal state first (the last shape read 30 % low right after 16384^3)
+        lib_fn, lib_note = library_fp4_mm(qa, qb)
+        fns = {"fp4": lambda: Q.nvfp4_mm(qa, qb.t(), out=d), "bf16": lambda: torch.matmul(A, Bt.t(), out=d)}
+        lib_check = None
+        if lib_fn is not None:
+            fns["cublaslt_fp4"] = lib_fn
+            ours = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.float32)
+            theirs = lib_fn().float()
+            if "only" in lib_note:
+                theirs = theirs * (qa.per_tensor_scale * qb.per_tensor_scale)
+            lib_check = float((theirs - ours).norm() / ours.norm())       # the comparator computes the same product
+            del ours, theirs
+        flops = 2.0 * m * n * k
+        rec = {"m": m, "n": n, "k": k, "library": lib_note, "library_vs_ours_rel_diff": lib_check}
+        for name, fn in fns.items():
+            # burst: single launches; let the previous seconds of dense GEMMs drain out of the
+            # power/thermal state first (a shape read 30 % low right after the 16384^3 runs)
             torch.cuda.synchronize()
             time.sleep(1.0)
-            for i in range(3):
-                fn(i)
+            for _ in range(3):
+                fn()
             ts = []
-            for i in range(10):
+            for _ in range(10):
                 flush.zero_()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(); fn(i); e1.record(); e1.synchronize()
+                e0.record(); fn(); e1.record(); e1.synchronize()
                 ts.append(e0.elapsed_time(e1))
-            res[name] = 2.0 * m * n * k / (statistics.median(ts) * 1e-3) / 1e12
-        out["gemm"].append({"m": m, "n": n, "k": k, "fp4_tflops": res["fp4"], "bf16_tflops": res["bf16"],
-                            "frac_of_4x_bf16_peak": res["fp4"] / (4 * bf16_peak),
-                            "frac_of_9pf_datasheet": res["fp4"] / 9000.0})
-        del A, Bt, qa, qb, d
+            burst_ms = statistics.median(ts)
+            # sustained: back to back for about a second, under the power cap
+            reps = max(5, min(4000, int(1000.0 / burst_ms)))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record(); e1.synchronize()
+            rec[f"{name}_tflops"] = flops / (burst_ms * 1e-3) / 1e12
+            rec[f"{name}_tflops_sustained"] = flops / (e0.elapsed_time(e1) / reps * 1e-3) / 1e12
+        rec["frac_of_4x_bf16_peak"] = rec["fp4_tflops"] / (4 * bf16_peak)
+        rec["frac_of_9pf_datasheet"] = rec["fp4_tflops"] / 9000.0
+        out["gemm"].append(rec)
+        del A, Bt, qa, qb, d, fns, lib_fn
     out["gemm_peak_kind"] = f"4 x {peak_kind} bf16 burst ({bf16_peak} TF/s)"
     del flush
     torch.cuda.empty_cache()

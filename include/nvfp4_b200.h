@@ -200,6 +200,22 @@ int nvfp4_relu2_bwd_bf16(const void* x, const void* dout, int64_t rows, int64_t 
                          void* dx, int64_t ld_out, const float* signs16, float* maxima2, int zero_first,
                          void* stream);
 
+/*
+ * Test hooks of the bounded waits, process-wide, for the launches that follow.  Every spin inside
+ * the kernels (grid barrier, mbarrier) gives up after a time limit, records a code (workspace word
+ * 4 / the static error word for the quantizer, *status for the GEMM) and lets the kernel drain and
+ * return; these hooks let a test make that happen in a millisecond instead of never:
+ *   wait_limit_ns                    the limit (0 = the default, 2 s)
+ *   quantizer_extra_arrivals         the quantizer's grid barrier expects this many arrivals more
+ *                                    than the grid has CTAs, so it can only run out (code 1)
+ *   gemm_drop_first_scale_arrival    != 0: the scale-factor warps never announce K slice 0, so the
+ *                                    MMA issuer's first wait runs out (code 2) and every role leaves
+ * nvfp4_test_hooks(0, 0, 0) restores normal operation.  No GPU fault, trap or endless loop is
+ * involved: the kernels return through their documented give-up path.  No counterpart in the
+ * reference.
+ */
+int nvfp4_test_hooks(uint64_t wait_limit_ns, int quantizer_extra_arrivals, int gemm_drop_first_scale_arrival);
+
 #ifdef __cplusplus
 }
 #endif

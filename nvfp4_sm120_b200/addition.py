@@ -40,7 +40,32 @@ def split_pairs():
     return perm[100_000:], perm[:100_000]
 
 
+_PAIR_LISTS = {}
+
+
+def pair_tuples(idx):
+    """Pair indices -> the reference's form, a list of (a, b) tuples (nvfp4_validate.py:247-255);
+    the list is remembered so that as_pair_indices finds its tensor again without a conversion."""
+    out = list(zip((idx // 1000).tolist(), (idx % 1000).tolist()))
+    _PAIR_LISTS[id(out)] = (out, idx)
+    return out
+
+
+def as_pair_indices(pairs):
+    """A tensor of pair indices 1000 a + b, or a list of (a, b) tuples -> the index tensor."""
+    if isinstance(pairs, torch.Tensor):
+        return pairs
+    hit = _PAIR_LISTS.get(id(pairs))
+    if hit is not None and hit[0] is pairs:
+        return hit[1]
+    t = torch.tensor(pairs, dtype=torch.long)
+    idx = t[:, 0] * 1000 + t[:, 1]
+    _PAIR_LISTS[id(pairs)] = (pairs, idx)
+    return idx
+
+
 def make_batch(pairs, batch, gen, device):
+    pairs = as_pair_indices(pairs)
     pick = pairs[torch.randint(0, len(pairs), (batch,), generator=gen)]
     tok = encode(pick // 1000, pick % 1000).to(device)
     return tok[:, :-1], tok[:, 1:]

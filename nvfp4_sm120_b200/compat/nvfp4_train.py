@@ -47,8 +47,9 @@ def LM(vocab, dim, nl, nh, nkv, hd, ffn, use_fp4, hp_tail=0):
 
 
 def evaluate(model, val, g, n=8, bs=512):
-    """(held-out loss, exact-answer accuracy), nvfp4_train.py:143-156; `val` = held-out pair indices."""
-    return _addition.evaluate(model, val, g, DEV, batches=n, batch=bs)
+    """(held-out loss, exact-answer accuracy), nvfp4_train.py:143-156; `val` = the held-out pairs as
+    nvfp4_validate.build_dataset returns them (a list of (a, b) tuples) or as a tensor of pair indices."""
+    return _addition.evaluate(model, _addition.as_pair_indices(val), g, DEV, batches=n, batch=bs)
 
 
 def run(tag, steps, use_fp4, hp_tail=0, seed=0):

@@ -72,6 +72,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); mbar_init(sf_bar(s), 4); }
     mbar_init(acc_bar, 1);
     *abort_flag = 0;
+    set_wait_limit(abort_flag, p.wait_limit_ns);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -194,7 +195,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(sf_bar(s));
+      if (lane == 0 && !(p.drop_first_scale_arrival && kt == 0)) mbar_arrive(sf_bar(s));
     }
     if (ok && lane == 0) {
       ok = mbar_wait(acc_bar, 0, abort_flag);

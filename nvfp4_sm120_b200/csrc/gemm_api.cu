@@ -13,6 +13,15 @@ int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtens
 #include <atomic>
 
 static std::atomic<int> g_gemm_mode{0};
+// test hooks (nvfp4_test_hooks): the wait limit of the next launches and the dropped arrival
+static std::atomic<unsigned long long> g_gemm_wait_ns{0};
+static std::atomic<int> g_gemm_drop_arrival{0};
+namespace nvfp4 { namespace gemm {
+void set_test_hooks(unsigned long long wait_ns, int drop_arrival) {
+  g_gemm_wait_ns.store(wait_ns, std::memory_order_relaxed);
+  g_gemm_drop_arrival.store(drop_arrival, std::memory_order_relaxed);
+}
+}}
 extern "C" int nvfp4_gemm_set_mode(int mode) {
   if (mode < 0 || mode > 2) return NVFP4_E_MODE;
   g_gemm_mode.store(mode, std::memory_order_relaxed);
@@ -42,7 +51,8 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
   CUtensorMap map_a, map_b;
   if (!make_operand_map(&map_a, a_q, M, K, 128) || !make_operand_map(&map_b, b_q, N, K, pair ? 128 : 256))
     return NVFP4_E_DRIVER;
-  Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status, 1, 0};
+  Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status, 1, 0,
+           g_gemm_wait_ns.load(std::memory_order_relaxed), g_gemm_drop_arrival.load(std::memory_order_relaxed)};
   // Split K when a small fp32 output (the weight gradient: few tiles, K = tokens) would leave most SMs
   // idle: the CTAs of a tile add their partial sums into the zeroed output.  Summation order then
   // varies from run to run in the last bits, so it is used only where it pays: fewer tiles than half

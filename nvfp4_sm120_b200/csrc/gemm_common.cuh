@@ -11,7 +11,7 @@ namespace gemm {
 constexpr int kTileK = 256;                 // elements per K slice = 128 bytes per operand row
 constexpr int kTmemCols = 512;
 constexpr int kGroupM = 32;                 // row tiles per rasterization group (32 measured 1-3 % above 16, 8 below)
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // a wait that lasts 2 s gives up
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // a wait that lasts 2 s gives up (the default)
 
 enum : int { kErrProducerWait = 1, kErrMmaWait = 2, kErrEpilogueWait = 3, kErrScaleWait = 4 };
 
@@ -40,14 +40,22 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+// The CTA keeps its abort flag (int) and, 8 bytes behind it, the wait limit in nanoseconds (the
+// launch's Params::wait_limit_ns, written by thread 0 before the first wait) in shared memory.
+__device__ __forceinline__ unsigned long long wait_limit_of(volatile int* abort_flag) {
+  return *reinterpret_cast<volatile unsigned long long*>(const_cast<int*>(abort_flag) + 2);
+}
+__device__ __forceinline__ void set_wait_limit(volatile int* abort_flag, unsigned long long ns) {
+  *reinterpret_cast<volatile unsigned long long*>(const_cast<int*>(abort_flag) + 2) = ns != 0 ? ns : kWaitLimitNs;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
+  const unsigned long long t0 = global_ns(), limit = wait_limit_of(abort_flag);
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 0u) {
       if (*abort_flag != 0) return false;
-      if (global_ns() - t0 > kWaitLimitNs) return false;
+      if (global_ns() - t0 > limit) return false;
     }
   }
 }
@@ -55,13 +63,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // does not take issue slots from the warps of its scheduler that feed the tensor pipe.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = global_ns();
+  const unsigned long long t0 = global_ns(), limit = wait_limit_of(abort_flag);
   for (uint32_t i = 1;; ++i) {
     __nanosleep(64);
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0u) {
       if (*abort_flag != 0) return false;
-      if (global_ns() - t0 > kWaitLimitNs) return false;
+      if (global_ns() - t0 > limit) return false;
     }
   }
 }
@@ -137,6 +145,9 @@ struct Params {
   int splits;        // > 1: K is split over `splits` CTAs per tile, which add their partial sums into
                      // a zeroed fp32 output with atomics (one-CTA kernel only)
   int tma_store;     // the output goes through shared memory and TMA stores (needs a 16-byte row pitch)
+  unsigned long long wait_limit_ns;   // every bounded wait gives up after this long (0 = kWaitLimitNs)
+  int drop_first_scale_arrival;       // test hook: the scale warps never announce K slice 0, so the MMA
+                                      // issuer's first wait runs out and the kernel takes its abort path
 };
 
 __device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status, int code) {

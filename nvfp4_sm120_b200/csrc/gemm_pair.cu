@@ -126,6 +126,7 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 16);
     *abort_flag = 0;
+    set_wait_limit(abort_flag, p.wait_limit_ns);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -282,7 +283,9 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) { if (leader) mbar_arrive(sready_bar(s)); else mbar_arrive_cluster(leader_ready0 + 8u * s); }
+      if (lane == 0 && !(p.drop_first_scale_arrival && g == 0)) {
+        if (leader) mbar_arrive(sready_bar(s)); else mbar_arrive_cluster(leader_ready0 + 8u * s);
+      }
     }
   } else {
     // ------------------------------ epilogue ------------------------------

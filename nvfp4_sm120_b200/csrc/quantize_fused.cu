@@ -14,6 +14,7 @@
 // memory-bound: the block scale (amax_b/6)/pts is first formed as one multiply and accepted only
 // when its E4M3 rounding provably equals that of the two true divisions (else those are done),
 // and (1/pts)/scale comes from a 128-entry table built per CTA with true divisions.
+#include <atomic>
 #include <cstddef>
 #include <mutex>
 
@@ -30,7 +31,7 @@ constexpr int kStashBytes = kChunkBytes * kMaxChunks;
 constexpr int kTabBlocks = 16384;                  // block maxima of phase 1 kept for phase 2 (2 B each)
 constexpr int kMiscOff = kStashBytes + 2 * kTabBlocks;
 constexpr int kSmemBytes = kMiscOff + 1024;        // + reciprocal table, barrier, reduction scratch
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // default of the bounded waits: 2 s
 constexpr int kBatch = 4;                          // blocks per thread in flight, amax pass
 constexpr int kBatch2 = 2;                         // same, quantize pass (register budget: 64)
 
@@ -180,7 +181,9 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
                    FastDiv div_bpr, const float* __restrict__ signs16, PhiloxKeys keys, uint64_t offset,
                    uint8_t* __restrict__ qdata, uint8_t* __restrict__ scales, float* __restrict__ pts_out,
                    Workspace* __restrict__ ws, uint32_t blocks_per_cta, int contiguous,
-                   const float* __restrict__ amax_in) {
+                   const float* __restrict__ amax_in, unsigned long long wait_limit_ns, uint32_t extra_arrivals) {
+  // wait_limit_ns: after this long a bounded wait gives up.  extra_arrivals (test hook, normally 0):
+  // the grid barrier expects that many arrivals more than there are CTAs, so it can only run out.
   // KNOWN: the caller knows the per-tensor maximum (a fused producer, or an all-reduce over a
   // sharded tensor): no first pass, no grid barrier, no workspace; one streaming quantize pass.
   constexpr bool known = KNOWN;
@@ -273,7 +276,7 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
     if (!landed) {
       const unsigned long long t0 = global_ns();
       while (!(landed = mbar_try_wait(bar, 0))) {
-        if (global_ns() - t0 > kWaitLimitNs) break;
+        if (global_ns() - t0 > wait_limit_ns) break;
       }
     }
     if (!landed) { *cta_abort = 1; ws->error = 2; }
@@ -323,8 +326,8 @@ quant_fused_kernel(const uint16_t* __restrict__ x, uint32_t rows, uint32_t blk_p
       uint32_t spins = 0;
       do {
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(&ws->arrived[slot]) : "memory");
-        if (seen >= gridDim.x) break;
-        if ((++spins & 63u) == 0u && global_ns() - t0 > kWaitLimitNs) { *cta_abort = 1; ws->error = 1; break; }
+        if (seen >= gridDim.x + extra_arrivals) break;
+        if ((++spins & 63u) == 0u && global_ns() - t0 > wait_limit_ns) { *cta_abort = 1; ws->error = 1; break; }
       } while (true);
       unsigned int amax_bits;
       asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(amax_bits) : "l"(amax_word) : "memory");
@@ -472,6 +475,9 @@ struct DeviceInfo {
 };
 std::mutex g_info_mutex;
 DeviceInfo g_info[kMaxDevices];
+// test hooks (nvfp4_test_hooks): wait limit of the next launches, surplus arrivals the barrier expects
+std::atomic<unsigned long long> g_wait_ns{0};
+std::atomic<unsigned int> g_extra_arrivals{0};
 
 const void* fused_fn(bool sr, bool rht, bool known) {
 #define NVFP4_FUSED_FN(K_, T_, B_) \
@@ -547,14 +553,27 @@ static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, i
     keys.k[r][0] = (uint32_t)seed + (uint32_t)r * 0x9E3779B9u;
     keys.k[r][1] = (uint32_t)(seed >> 32) + (uint32_t)r * 0xBB67AE85u;
   }
+  unsigned long long wait_ns = g_wait_ns.load(std::memory_order_relaxed);
+  if (wait_ns == 0) wait_ns = kWaitLimitNs;
+  uint32_t extra = g_extra_arrivals.load(std::memory_order_relaxed);
   void* args[] = {&xp, &rows32, &bpr, &ld, &fd, &signs16, &keys, &offset, &qdata, &scales, &pts_out, &ws, &per,
-                  &contiguous, &amax_in};
+                  &contiguous, &amax_in, &wait_ns, &extra};
   const cudaError_t e = known ? cudaLaunchKernel(fn, dim3(grid), dim3(kThreadsKnown), args, kSmemBytes, stream)
                               : cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(kThreads), args, kSmemBytes, stream);
   if (e != cudaSuccess) {
     cudaGetLastError();          // a refused launch must not show up as the next call's error
     return NVFP4_E_LAUNCH;
   }
+  return NVFP4_OK;
+}
+
+namespace nvfp4 { namespace gemm { void set_test_hooks(unsigned long long wait_ns, int drop_arrival); } }
+
+extern "C" int nvfp4_test_hooks(uint64_t wait_limit_ns, int quantizer_extra_arrivals, int gemm_drop_first_scale_arrival) {
+  if (quantizer_extra_arrivals < 0 || quantizer_extra_arrivals > 1024) return NVFP4_E_MODE;
+  g_wait_ns.store(wait_limit_ns, std::memory_order_relaxed);
+  g_extra_arrivals.store((unsigned int)quantizer_extra_arrivals, std::memory_order_relaxed);
+  nvfp4::gemm::set_test_hooks(wait_limit_ns, gemm_drop_first_scale_arrival != 0 ? 1 : 0);
   return NVFP4_OK;
 }
 

@@ -111,7 +111,14 @@ class FP4LinearFn(torch.autograd.Function):
         # passes over x would find); the token count must then be a multiple of 16
         if x_amax is not None and (x2.shape[0] % BLK != 0 or x2.dtype != torch.bfloat16):
             x_amax = None
-        xq = _quant(x2, amax_reduce if x_sharded else None, amax=None if x_amax is None else x_amax[0:1])
+        x_red = amax_reduce if x_sharded else None
+        if x_amax is not None and x_red is not None:
+            # both maxima of a sharded x in ONE collective; the backward reuses the second
+            x_amax = x_amax.clone()
+            x_red(x_amax)
+            x_red = None
+        ctx.x_reduced = x_amax is not None and x_sharded and amax_reduce is not None
+        xq = _quant(x2, x_red, amax=None if x_amax is None else x_amax[0:1])
         if wq_K is None:
             wq_K = _quant(w, amax_reduce)
         y = nvfp4_mm(xq, wq_K.t(), torch.bfloat16)
@@ -128,20 +135,28 @@ class FP4LinearFn(torch.autograd.Function):
         x_sharded, y_sharded = ctx.sharded
         gy2 = gy.reshape(-1, w.shape[0])
         g_amax, g_amax_rht = _take_grad_amax(gy2, signs)      # known to a fused producer of gy, else None
+        g_red = red if y_sharded else None
+        if g_amax is not None and g_red is not None:
+            # a sharded gradient: reduce the producer's maxima over the group, both in ONE collective
+            both = torch.cat([g_amax, g_amax_rht]) if g_amax_rht is not None else g_amax.clone()
+            g_red(both)
+            g_amax, g_amax_rht = both[0:1], (both[1:2] if g_amax_rht is not None else None)
         x_amax_rht = None if (ctx.x_amax is None or not ctx.x_amax_rht) else ctx.x_amax[1:2]
+        # the Hadamard maximum of a sharded x was reduced in forward together with the plain one;
+        # when it has to be recomputed here (none given, or another sign vector) it is reduced here
+        xt_red = None if (x_amax_rht is not None and ctx.x_reduced) else (red if x_sharded else None)
         dx = dw = None
         if ctx.needs_input_grad[0]:
             # dgrad: dX = dY @ W, contraction over N; dY gets stochastic rounding
-            gq = _quant(gy2, red if y_sharded else None, stochastic=True, amax=g_amax)
+            gq = _quant(gy2, None if g_amax is not None else g_red, stochastic=True, amax=g_amax)
             if wq_N is None:
                 wq_N = _quant(w, red, transpose=True)
             dx = nvfp4_mm(gq, wq_N.t(), torch.bfloat16).reshape(ctx.xshape).to(gy.dtype)
         if ctx.needs_input_grad[1]:
             # wgrad: dW = dY^T @ X, contraction over tokens; Hadamard on both, SR on the gradient
-            gtq = _quant(gy2, red if y_sharded else None, stochastic=True, rht=True, H=H, signs=signs,
+            gtq = _quant(gy2, None if g_amax_rht is not None else g_red, stochastic=True, rht=True, H=H, signs=signs,
                          transpose=True, amax=g_amax_rht)
-            xtq = _quant(x2, red if x_sharded else None, rht=True, H=H, signs=signs, transpose=True,
-                         amax=x_amax_rht)
+            xtq = _quant(x2, xt_red, rht=True, H=H, signs=signs, transpose=True, amax=x_amax_rht)
             dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
         return dx, dw, None, None, None, None, None, None, None, None
 

@@ -26,7 +26,9 @@ class GPTConfig:
     n_kv_heads: int = 12
     mlp_ratio: int = 4
     use_fp4: bool = True
-    hp_tail: int = 1           # last blocks kept dense; block 0 always is (scaling/train_text.py:66-67)
+    hp_tail: int = 1           # last blocks kept dense (scaling/train_text.py:66-67)
+    dense_first: bool = True   # block 0 kept dense, the reference's rule; False + hp_tail 0 = every
+                               # linear of every block in FP4 (benchmark config 5 as written)
     tie_head: bool = True
 
 
@@ -87,7 +89,7 @@ class GPT(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.emb = nn.Embedding(cfg.vocab, cfg.dim, device=device)
-        fp4_at = lambda i: cfg.use_fp4 and not (i == 0 or i >= cfg.n_layers - cfg.hp_tail)
+        fp4_at = lambda i: cfg.use_fp4 and not ((i == 0 and cfg.dense_first) or i >= cfg.n_layers - cfg.hp_tail)
         self.blocks = nn.ModuleList(
             DecoderBlock(cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.mlp_ratio * cfg.dim, fp4_at(i), device)
             for i in range(cfg.n_layers))

@@ -120,8 +120,11 @@ class ColumnParallelFP4Linear(_ParallelLinearBase):
     """y_local[*, out/p] = x @ W_local^T.  x is replicated; the output and its gradient are split
     along the feature dim, so their amax is reduced; dX is summed over the group."""
 
-    def forward(self, x):
-        x = _CopyToGroup.apply(x, self.group)
+    def forward(self, x, copied=False):
+        """copied: x already went through the group's copy (the caller feeds several column-parallel
+        layers from one copy so that their input gradients are summed locally and all-reduced once)."""
+        if not copied:
+            x = _CopyToGroup.apply(x, self.group)
         return self._call(x, (False, True))
 
 
@@ -153,7 +156,10 @@ class TensorParallelSwiGLU(nn.Module):
                    shard_cols(full_down, rank, world), group, linear_fn, device)
 
     def forward(self, x):
-        g, u = self.gate(x), self.up(x)
+        # one copy-to-group for both projections: autograd adds gate's and up's input gradients
+        # locally and the sum crosses the links once
+        xc = _CopyToGroup.apply(x, self.gate.group)
+        g, u = self.gate(xc, copied=True), self.up(xc, copied=True)
         if self.gate.linear_fn is _fp4_linear_fn and g.is_cuda and g.dtype == torch.bfloat16:
             # fused SwiGLU: the maxima it leaves are this rank's; the linears reduce them over the group
             from .swiglu import swiglu
@@ -202,6 +208,86 @@ def all_reduce_gradients(params, group=None, bucket_bytes: int = 64 << 20, wire_
         if size >= bucket_bytes:
             flush()
     flush()
+
+
+class GradientReducer:
+    """Data-parallel gradient averaging overlapped with the backward pass.
+
+    The parameters are cut into buckets of about `bucket_bytes` in the order the backward pass
+    finishes them (reverse registration order).  Every parameter gets a post-accumulate hook; once
+    `arm()` has been called (before the backward of the LAST microbatch of a step) the hook counts
+    the bucket down, and the bucket whose last gradient has just been accumulated is packed into one
+    `wire_dtype` buffer (bf16 on the wire, as the data-parallel benchmark config asks) and all-reduced
+    asynchronously: NCCL runs it on its own stream while the main stream goes on with the rest of the
+    backward.  `finish()` launches what is left (parameters that received no gradient are skipped),
+    waits, divides by the group size and writes the averages back in the gradients' own dtype."""
+
+    def __init__(self, params, group=None, bucket_bytes: int = 32 << 20, wire_dtype=torch.bfloat16):
+        self.group, self.wire_dtype = group, wire_dtype
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        esize = torch.empty((), dtype=wire_dtype).element_size()
+        self.buckets, cur, size = [], [], 0
+        seen = set()
+        for p in reversed([p for p in params if p.requires_grad]):
+            if id(p) in seen:                      # a tied parameter appears once
+                continue
+            seen.add(id(p))
+            cur.append(p)
+            size += p.numel() * esize
+            if size >= bucket_bytes:
+                self.buckets.append(cur)
+                cur, size = [], 0
+        if cur:
+            self.buckets.append(cur)
+        self._bucket_of = {id(p): i for i, b in enumerate(self.buckets) for p in b}
+        self._pending, self._inflight, self._armed = [], {}, False
+        self._handles = [p.register_post_accumulate_grad_hook(self._on_grad) for b in self.buckets for p in b]
+
+    def arm(self):
+        """Call before the backward pass whose gradients are final (the last microbatch)."""
+        self._pending = [len(b) for b in self.buckets]
+        self._inflight = {}
+        self._armed = True
+
+    def _on_grad(self, p):
+        if not self._armed:
+            return
+        i = self._bucket_of[id(p)]
+        self._pending[i] -= 1
+        if self._pending[i] == 0:
+            self._launch(i)
+
+    def _launch(self, i):
+        ps = [p for p in self.buckets[i] if p.grad is not None]
+        if not ps:
+            return
+        flat = torch.cat([p.grad.reshape(-1).to(self.wire_dtype) for p in ps])
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True) if self.world > 1 else None
+        self._inflight[i] = (ps, flat, work)
+
+    def finish(self):
+        """Wait for every bucket and store the averaged gradients."""
+        if not self._armed:
+            raise RuntimeError("GradientReducer.finish() without arm()")
+        self._armed = False
+        for i in range(len(self.buckets)):
+            if i not in self._inflight:
+                self._launch(i)                    # a bucket some gradient never reached
+        for i in sorted(self._inflight):
+            ps, flat, work = self._inflight[i]
+            if work is not None:
+                work.wait()
+            off = 0
+            for p in ps:
+                n = p.numel()
+                p.grad.copy_(flat[off:off + n].view_as(p.grad).to(p.grad.dtype).div_(self.world))
+                off += n
+        self._inflight = {}
+
+    def remove(self):
+        for h in self._handles:
+            h.remove()
+        self._handles = []
 
 
 def seed_stochastic_rounding(base_seed: int, rank: int):

@@ -50,6 +50,59 @@ def lr_at(step, base, warmup, total):
     return base * (0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi * t)))
 
 
+class Trainer:
+    """One data-parallel replica of the config-5 training job: model, AdamW, synthetic sampler and
+    the optimizer step (gradient accumulation over microbatches, gradient averaging over the group
+    overlapped with the last backward, clipping, AdamW, weight-quant cache refresh)."""
+
+    def __init__(self, dev, rank=0, world=1, backend="fp4", vocab=50257, dim=768, layers=12, heads=12, seq=1024,
+                 global_batch=256, micro_batch=16, lr=6e-4, warmup=15, total_steps=300, all_fp4=False,
+                 overlap=True, group=None):
+        self.dev, self.rank, self.world, self.seq = dev, rank, world, seq
+        self.lr, self.warmup, self.total_steps, self.global_batch = lr, warmup, total_steps, global_batch
+        linear.set_amortize(True)                      # weights are quantized once per optimizer step
+        torch.manual_seed(0)
+        # all_fp4: every linear of every block (benchmark config 5 as written, 72 linears at 12 layers);
+        # otherwise the reference's placement rule: block 0 and the last block stay dense
+        cfg = GPTConfig(vocab=vocab, dim=dim, n_layers=layers, n_heads=heads, n_kv_heads=heads,
+                        use_fp4=backend == "fp4", hp_tail=0 if all_fp4 else 1, dense_first=not all_fp4)
+        self.model = GPT(cfg, device=dev)
+        if world > 1:
+            parallel.broadcast_parameters(self.model)
+        parallel.seed_stochastic_rounding(1234, rank)
+        self.params = [p for p in self.model.parameters()]
+        self.opt = torch.optim.AdamW(self.params, lr=lr, betas=(0.9, 0.95), weight_decay=0.1, fused=dev.type == "cuda")
+        self.sample, self.entropy = zipf_sampler(vocab, 1.1, 5 + rank, dev)
+        per_rank = global_batch // world
+        assert per_rank % micro_batch == 0 and per_rank * world == global_batch
+        self.micro_batch, self.accum = micro_batch, per_rank // micro_batch
+        self.reducer = parallel.GradientReducer(self.params, group) if (world > 1 and overlap) else None
+        self.group = group
+
+    def step(self, step):
+        """Optimizer step number `step` (1-based); returns this rank's mean microbatch loss (a tensor)."""
+        for pg in self.opt.param_groups:
+            pg["lr"] = lr_at(step, self.lr, self.warmup, self.total_steps)
+        self.opt.zero_grad(set_to_none=True)
+        loss_sum = torch.zeros((), device=self.dev)
+        for i in range(self.accum):
+            x, y = self.sample(self.micro_batch, self.seq)
+            with torch.autocast(self.dev.type, dtype=torch.bfloat16):
+                _, loss = self.model(x, y)
+            if self.reducer is not None and i == self.accum - 1:
+                self.reducer.arm()                     # these gradients are final: reduce them as they appear
+            (loss / self.accum).backward()
+            loss_sum += loss.detach() / self.accum
+        if self.reducer is not None:
+            self.reducer.finish()
+        elif self.world > 1:
+            parallel.all_reduce_gradients(self.params, self.group)
+        torch.nn.utils.clip_grad_norm_(self.params, 1.0)
+        self.opt.step()
+        linear.mark_step()
+        return loss_sum
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--backend", default="fp4", choices=["fp4", "bf16"])
@@ -64,6 +117,9 @@ def main():
     ap.add_argument("--lr", type=float, default=6e-4)
     ap.add_argument("--warmup", type=int, default=15)
     ap.add_argument("--log-every", type=int, default=10)
+    ap.add_argument("--all-fp4", action="store_true",
+                    help="every linear of every block in FP4 (default: block 0 and the last block stay dense)")
+    ap.add_argument("--no-overlap", action="store_true", help="reduce the gradients after the backward pass")
     ap.add_argument("--out", default=None, help="append the JSON lines to this file too")
     a = ap.parse_args()
 
@@ -74,19 +130,8 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    linear.set_amortize(True)                      # weights are quantized once per optimizer step
-    torch.manual_seed(0)
-    model = GPT(GPTConfig(vocab=a.vocab, dim=a.dim, n_layers=a.layers, n_heads=a.heads, n_kv_heads=a.heads,
-                          use_fp4=a.backend == "fp4"), device=dev)
-    if world > 1:
-        parallel.broadcast_parameters(model)
-    parallel.seed_stochastic_rounding(1234, rank)
-    opt = torch.optim.AdamW(model.parameters(), lr=a.lr, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
-    sample, entropy = zipf_sampler(a.vocab, 1.1, 5 + rank, dev)
-    per_rank = a.global_batch // world
-    assert per_rank % a.micro_batch == 0 and per_rank * world == a.global_batch
-    accum = per_rank // a.micro_batch
-    params = [p for p in model.parameters()]
+    tr = Trainer(dev, rank, world, a.backend, a.vocab, a.dim, a.layers, a.heads, a.seq, a.global_batch, a.micro_batch,
+                 a.lr, a.warmup, a.steps, a.all_fp4, not a.no_overlap)
 
     def emit(rec):
         if rank == 0:
@@ -96,29 +141,16 @@ def main():
                 with open(a.out, "a") as f:
                     f.write(line + "\n")
 
-    emit({"event": "start", "backend": a.backend, "params_non_embedding": model.num_params(), "world": world,
-          "tokens_per_step": a.global_batch * a.seq, "fp4_linears": len(model.fp4_linears()),
-          "zipf_entropy_nats": entropy})
+    emit({"event": "start", "backend": a.backend, "params_non_embedding": tr.model.num_params(), "world": world,
+          "tokens_per_step": a.global_batch * a.seq, "fp4_linears": len(tr.model.fp4_linears()),
+          "zipf_entropy_nats": tr.entropy})
     t_start = None
+    loss_sum = torch.zeros((), device=dev)
     for step in range(1, a.steps + 1):
         if step == 3:
             torch.cuda.synchronize()
             t_start = time.perf_counter()
-        for pg in opt.param_groups:
-            pg["lr"] = lr_at(step, a.lr, a.warmup, a.steps)
-        opt.zero_grad(set_to_none=True)
-        loss_sum = torch.zeros((), device=dev)
-        for _ in range(accum):
-            x, y = sample(a.micro_batch, a.seq)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                _, loss = model(x, y)
-            (loss / accum).backward()
-            loss_sum += loss.detach() / accum
-        if world > 1:
-            parallel.all_reduce_gradients(params)
-        torch.nn.utils.clip_grad_norm_(params, 1.0)
-        opt.step()
-        linear.mark_step()
+        loss_sum = tr.step(step)
         if step % a.log_every == 0 or step == a.steps or step == 1:
             if world > 1:
                 dist.all_reduce(loss_sum)

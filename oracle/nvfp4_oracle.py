@@ -167,6 +167,21 @@ def round_e2m1_reference(x: torch.Tensor, stochastic: bool,
     return sgn * q
 
 
+def _in_row_chunks(fn, n_rows: int, *arrays, min_rows: int = 1 << 16):
+    """fn(*[a[r0:r1] for a in arrays]) over row chunks on a thread pool (numpy releases the
+    GIL), results concatenated: the same values as one call, only faster on large inputs."""
+    if n_rows < 2 * min_rows:
+        return fn(*arrays)
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+    workers = max(1, min(os.cpu_count() or 1, 32))
+    step = max(min_rows, -(-n_rows // (4 * workers)))
+    spans = [(r0, min(n_rows, r0 + step)) for r0 in range(0, n_rows, step)]
+    with ThreadPoolExecutor(workers) as pool:
+        parts = list(pool.map(lambda sp: fn(*[a[sp[0]:sp[1]] for a in arrays]), spans))
+    return np.concatenate(parts, axis=0)
+
+
 def philox4x32_10(counter: np.ndarray, key: np.ndarray) -> np.ndarray:
     """Philox-4x32 with 10 rounds (Salmon et al., SC'11).  counter: uint32
     [..., 4], key: uint32 [2] (or broadcastable [..., 2]).  Returns uint32 [..., 4]."""
@@ -200,7 +215,7 @@ def philox_block_bits(n_blocks: int, seed: int, offset: int) -> np.ndarray:
     ctr[:, 2] = np.uint32(offset & 0xFFFFFFFF)
     ctr[:, 3] = np.uint32((offset >> 32) & 0xFFFFFFFF)
     key = np.array([seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF], dtype=np.uint32)
-    return philox4x32_10(ctr, key)
+    return _in_row_chunks(lambda c: philox4x32_10(c, key), n_blocks, ctr)
 
 
 def _rev16(v: np.ndarray) -> np.ndarray:
@@ -237,6 +252,9 @@ def cvt_rs_e2m1x4(x: np.ndarray, rbits: np.ndarray) -> np.ndarray:
     element's 16-bit value from cvt_rs_fields(); |x| >= 6 saturates; the sign bit is
     the sign bit of x."""
     x = np.asarray(x, dtype=np.float32)
+    rbits = np.asarray(rbits)
+    if x.ndim >= 2 and x.shape[0] >= (1 << 17) and rbits.shape[0] == x.shape[0]:
+        return _in_row_chunks(cvt_rs_e2m1x4, x.shape[0], x, rbits)
     lv = np.array(E2M1_LEVELS, dtype=np.float32)
     m = np.minimum(np.abs(x), np.float32(6.0))
     idx = np.clip(np.searchsorted(lv, m, side="right"), 1, 7)

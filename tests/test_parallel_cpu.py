@@ -85,6 +85,35 @@ def _worker(rank, world, port, results):
     P.all_reduce_gradients(list(lin.parameters()), bucket_bytes=64)
     ok &= torch.allclose(lin.weight.grad, torch.full_like(lin.weight, (1 + world) / 2))
     ok &= torch.allclose(lin.bias.grad, torch.full_like(lin.bias, float(world - 1)))
+    # the same averages from the reducer that overlaps the exchange with the backward pass: hooks fire
+    # as gradients are accumulated, buckets go out as they fill, finish() stores the means
+    torch.manual_seed(3)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+    P.broadcast_parameters(net)
+    red = P.GradientReducer(list(net.parameters()), bucket_bytes=64)
+    ok &= len(red.buckets) >= 2
+    xin = torch.full((5, 8), float(rank + 1))
+    net(xin).sum().backward()                    # not armed: a microbatch before the last, nothing is sent
+    ok &= red._inflight == {}
+    red.arm()
+    net(xin).sum().backward()
+    local = [p.grad.clone() for p in net.parameters()]
+    red.finish()
+    for p, g in zip(net.parameters(), local):
+        both = [torch.empty_like(g) for _ in range(world)]
+        dist.all_gather(both, g)
+        ok &= torch.allclose(p.grad, torch.stack(both).mean(0), rtol=2e-2, atol=1e-3)      # bf16 on the wire
+    red.remove()
+    # a whole optimizer step of the trainer on two ranks: replicas stay identical
+    from nvfp4_sm120_b200.train import Trainer
+    tr = Trainer(torch.device("cpu"), rank, world, backend="bf16", vocab=61, dim=32, layers=2, heads=2, seq=8,
+                 global_batch=8, micro_batch=2, total_steps=4)
+    for st in range(1, 4):
+        tr.step(st)
+    w = tr.model.blocks[1].up.weight.detach().clone()
+    both = [torch.empty_like(w) for _ in range(world)]
+    dist.all_gather(both, w)
+    ok &= torch.equal(both[0], both[1]) and bool(torch.isfinite(w).all())
     results[rank] = bool(ok)
     dist.destroy_process_group()
 
