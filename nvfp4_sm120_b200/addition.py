@@ -86,15 +86,19 @@ def evaluate(model, held_out, gen, device, batches=8, batch=512):
     return loss_sum / batches, right / seen
 
 
-def run(tag, steps, use_fp4, hp_tail=0, seed=0, device="cuda", log=print):
-    """One training run with the reference's hyper-parameters (nvfp4_train.py:159-185)."""
+def run(tag, steps, use_fp4, hp_tail=0, seed=0, device="cuda", log=print, linear_factory=None, eval_every=None):
+    """One training run with the reference's hyper-parameters (nvfp4_train.py:159-185).
+    linear_factory: build the low-precision linears with this callable instead of FP4Linear (see
+    models.DecoderBlock); eval_every: held-out evaluation period in steps (default: six per run).
+    The returned record carries every evaluation in `history`."""
     torch.manual_seed(seed)
-    model = LM(len(VOCAB), 256, 6, 4, 2, 64, 768, use_fp4, hp_tail, device=device)
+    model = LM(len(VOCAB), 256, 6, 4, 2, 64, 768, use_fp4, hp_tail, device=device, linear_factory=linear_factory)
     train, held_out = split_pairs()
     opt = torch.optim.AdamW(model.parameters(), lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
     sched = torch.optim.lr_scheduler.OneCycleLR(opt, max_lr=1e-3, total_steps=steps, pct_start=0.05)
     gen = torch.Generator().manual_seed(seed + 7)
-    t0, last, diverged = time.time(), {}, False
+    t0, last, diverged, history = time.time(), {}, False, []
+    period = eval_every or max(1, steps // 6)
     for step in range(1, steps + 1):
         x, y = make_batch(train, 512, gen, device)
         with torch.autocast("cuda", dtype=torch.bfloat16):
@@ -109,11 +113,12 @@ def run(tag, steps, use_fp4, hp_tail=0, seed=0, device="cuda", log=print):
         opt.step()
         sched.step()
         linear.mark_step()
-        if step % max(1, steps // 6) == 0 or step == steps:
+        if step % period == 0 or step == steps:
             val, acc = evaluate(model, held_out, gen, device)
             last = {"step": step, "train": round(loss.item(), 4), "val": round(val, 4), "acc": round(acc, 4)}
+            history.append(last)
             log(json.dumps({"tag": tag, **last}))
-    out = {"tag": tag, "diverged": diverged, "seconds": round(time.time() - t0, 1), **last}
+    out = {"tag": tag, "diverged": diverged, "seconds": round(time.time() - t0, 1), **last, "history": history}
     log(json.dumps(out))
     return out
 

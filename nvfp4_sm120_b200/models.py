@@ -47,22 +47,30 @@ def apply_rotary(x, cos, sin):
 
 
 class DecoderBlock(nn.Module):
-    def __init__(self, dim, n_heads, n_kv_heads, hidden, use_fp4, device):
+    """linear_factory: optional callable (cin, cout) -> module that builds the block's low-precision
+    linears in place of FP4Linear (used to run the same model with another implementation of the
+    recipe, e.g. a fake-quant simulator, for loss-curve comparisons)."""
+
+    def __init__(self, dim, n_heads, n_kv_heads, hidden, use_fp4, device, linear_factory=None):
         super().__init__()
         assert dim % n_heads == 0 and n_heads % n_kv_heads == 0
         self.n_heads, self.n_kv, self.head_dim = n_heads, n_kv_heads, dim // n_heads
         self.norm_attn, self.norm_mlp = nn.RMSNorm(dim, device=device), nn.RMSNorm(dim, device=device)
         kv_dim = n_kv_heads * self.head_dim
-        self.q = make_linear(dim, dim, use_fp4, device)
-        self.k = make_linear(dim, kv_dim, use_fp4, device)
-        self.v = make_linear(dim, kv_dim, use_fp4, device)
-        self.o = make_linear(dim, dim, use_fp4, device)
-        self.up = make_linear(dim, hidden, use_fp4, device)
-        self.down = make_linear(hidden, dim, use_fp4, device)
+        if use_fp4 and linear_factory is not None:
+            mk = lambda cin, cout: linear_factory(cin, cout)
+        else:
+            mk = lambda cin, cout: make_linear(cin, cout, use_fp4, device)
+        self.q = mk(dim, dim)
+        self.k = mk(dim, kv_dim)
+        self.v = mk(dim, kv_dim)
+        self.o = mk(dim, dim)
+        self.up = mk(dim, hidden)
+        self.down = mk(hidden, dim)
         # the fused activation computes the Hadamard maxima for `down` and for `up`'s gradient with
         # `down`'s sign vector; a consumer holding another vector recomputes its maximum (checked at
         # call time: a checkpoint may change the buffers)
-        self.fused_act = bool(use_fp4)
+        self.fused_act = bool(use_fp4) and isinstance(self.up, FP4Linear) and isinstance(self.down, FP4Linear)
 
     def forward(self, x, cos, sin):
         B, T, _ = x.shape
@@ -85,13 +93,13 @@ class DecoderBlock(nn.Module):
 
 
 class GPT(nn.Module):
-    def __init__(self, cfg: GPTConfig, device="cuda"):
+    def __init__(self, cfg: GPTConfig, device="cuda", linear_factory=None):
         super().__init__()
         self.cfg = cfg
         self.emb = nn.Embedding(cfg.vocab, cfg.dim, device=device)
         fp4_at = lambda i: cfg.use_fp4 and not ((i == 0 and cfg.dense_first) or i >= cfg.n_layers - cfg.hp_tail)
         self.blocks = nn.ModuleList(
-            DecoderBlock(cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.mlp_ratio * cfg.dim, fp4_at(i), device)
+            DecoderBlock(cfg.dim, cfg.n_heads, cfg.n_kv_heads, cfg.mlp_ratio * cfg.dim, fp4_at(i), device, linear_factory)
             for i in range(cfg.n_layers))
         self.norm = nn.RMSNorm(cfg.dim, device=device)
         self.head = nn.Linear(cfg.dim, cfg.vocab, bias=False, device=device)
@@ -128,10 +136,11 @@ class LM(GPT):
     """The addition-task model of nvfp4_train.py:126-140: untied head, hp_tail counted from the end,
     block 0 dense when FP4 is on."""
 
-    def __init__(self, vocab, dim, nl, nh, nkv, hd, ffn, use_fp4, hp_tail=0, device="cuda"):
+    def __init__(self, vocab, dim, nl, nh, nkv, hd, ffn, use_fp4, hp_tail=0, device="cuda", linear_factory=None):
         assert hd * nh == dim and ffn % dim == 0
         super().__init__(GPTConfig(vocab=vocab, dim=dim, n_layers=nl, n_heads=nh, n_kv_heads=nkv,
-                                   mlp_ratio=ffn // dim, use_fp4=use_fp4, hp_tail=hp_tail, tie_head=False), device)
+                                   mlp_ratio=ffn // dim, use_fp4=use_fp4, hp_tail=hp_tail, tie_head=False), device,
+                         linear_factory)
 
     def forward(self, idx):
         return super().forward(idx)[0]

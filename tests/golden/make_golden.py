@@ -4,8 +4,9 @@ code on the CPU.  Run once, in a container that has the reference checkout:
     python tests/golden/make_golden.py /path/to/reference
 
 What runs: the reference's `nvfp4_gemm.quant_nvfp4`, `nvfp4_gemm.hadamard16`,
-`nvfp4_validate._round_e2m1`, `nvfp4_validate.quantize_nvfp4_1d` and
-`nvfp4_validate.apply_rht_lastdim`, unmodified, imported from that path.
+`nvfp4_validate._round_e2m1`, `nvfp4_validate.quantize_nvfp4_1d`, `quantize_nvfp4_2d`,
+`apply_rht_lastdim` and the simulator autograd `_NVFP4LinearFn` (forward and backward),
+unmodified, imported from that path.
 `nvfp4_gemm` imports four helpers from the third-party package torchao, which is
 not installed; they are stood in by the twins torch itself ships for its own
 tests (`torch.testing._internal.common_quantized`: `_f32_to_floatx_unpacked`,
@@ -147,6 +148,29 @@ def main(ref_path):
     x = cases["a_128x256"]
     out["a_128x256.sim1d"] = V.quantize_nvfp4_1d(x.float())
     out["a_128x256.rht_apply"] = V.apply_rht_lastdim(x.float(), V._hadamard16("cpu", torch.float32), signs1)
+
+    # the simulator's 16x16 weight scaling, and one forward + backward of its linear (the "reference
+    # recipe": x 1-D RNE, w 2-D RNE, dY stochastic, wgrad through the Hadamard with the token dim
+    # padded from 40 to 48) with the two uniform draws of the backward pass fixed
+    gw = torch.Generator().manual_seed(21)
+    w = torch.randn(48, 64, generator=gw) * 0.02
+    out["sim.w"] = w
+    out["sim.w2d"] = V.quantize_nvfp4_2d(w)
+    xs = torch.randn(40, 64, generator=gw)
+    gys = torch.randn(40, 48, generator=gw) * 1e-2
+    u_dgrad = torch.rand(40, 48, generator=gw)            # drawn for quantize_nvfp4_1d(gy): blocks [40, 3, 16]
+    u_wgrad = torch.rand(48, 48, generator=gw)            # drawn for quantize_nvfp4_1d(gy^T padded): [48, 3, 16]
+    pool = {(40, 3, 16): u_dgrad.reshape(40, 3, 16), (48, 3, 16): u_wgrad.reshape(48, 3, 16)}
+    torch.rand_like = lambda m: pool[tuple(m.shape)]
+    try:
+        cfg = {"sr": True, "rht": True}
+        xr, wr = xs.clone().requires_grad_(True), w.clone().requires_grad_(True)
+        y = V._NVFP4LinearFn.apply(xr, wr, cfg, V._hadamard16("cpu", torch.float32), signs1)
+        y.backward(gys)
+    finally:
+        torch.rand_like = real_rand_like
+    out["sim.x"], out["sim.gy"], out["sim.u_dgrad"], out["sim.u_wgrad"] = xs, gys, u_dgrad, u_wgrad
+    out["sim.y"], out["sim.dx"], out["sim.dw"] = y.detach(), xr.grad.clone(), wr.grad.clone()
 
     dst = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden_quant.pt")
     torch.save(out, dst)

@@ -177,3 +177,47 @@ def test_cvt_rs_model_matches_reference_rule():
     u = torch.from_numpy(O.cvt_rs_equivalent_uniforms(rbits))
     ref = O.e2m1_encode_rne(O.round_e2m1_reference(torch.from_numpy(x), True, u)).numpy()
     assert np.array_equal(hw, ref)
+
+
+# ---------------------------------------------------------------------------------------------
+# the reference's training recipe as a simulator (oracle/nvfp4_sim.py) against the reference's own
+# quantize_nvfp4_1d / quantize_nvfp4_2d / apply_rht_lastdim / _NVFP4LinearFn
+# ---------------------------------------------------------------------------------------------
+def test_simulator_quantizers_match_reference(golden):
+    from oracle import nvfp4_sim as S
+    x = golden["a_128x256.x"].float()
+    assert torch.equal(S.quantize_1d(x), golden["a_128x256.sim1d"])
+    assert torch.equal(S.rht_lastdim(x, S.hadamard16("cpu"), O.signs_from_seed(1)), golden["a_128x256.rht_apply"])
+    w2d = S.quantize_2d(golden["sim.w"])
+    assert torch.equal(w2d, golden["sim.w2d"])
+    # the point of the 16x16 scaling: the transposed weight quantizes to the transposed values
+    assert torch.equal(S.quantize_2d(golden["sim.w"].t().contiguous()), w2d.t())
+    grid, u = golden["round.grid"], golden["round.u"]
+    assert torch.equal(S.snap_e2m1(grid, True, u), golden["round.sr"])
+    assert torch.equal(S.snap_e2m1(grid, False), golden["round.rn"])
+
+
+def test_simulator_linear_forward_backward_match_reference(golden, monkeypatch):
+    """One forward + backward of the recipe (x 1-D RNE, w 2-D RNE, dY stochastic, wgrad through the
+    Hadamard with 40 tokens padded to 48), fed the uniforms the reference run was fed."""
+    from oracle import nvfp4_sim as S
+    pool = {(40, 3, 16): golden["sim.u_dgrad"].reshape(40, 3, 16), (48, 3, 16): golden["sim.u_wgrad"].reshape(48, 3, 16)}
+    monkeypatch.setattr(torch, "rand_like", lambda m: pool[tuple(m.shape)])
+    x = golden["sim.x"].clone().requires_grad_(True)
+    w = golden["sim.w"].clone().requires_grad_(True)
+    y = S.SimLinearFn.apply(x, w, True, True, S.hadamard16("cpu"), O.signs_from_seed(1))
+    y.backward(golden["sim.gy"])
+    assert torch.equal(y.detach(), golden["sim.y"])
+    assert torch.equal(x.grad, golden["sim.dx"])
+    assert torch.equal(w.grad, golden["sim.dw"])
+
+
+def test_simulator_tracks_the_real_fp4_recipe():
+    """The simulator and the real-FP4 oracle describe the same quantizer up to their documented
+    differences (tie direction, 2^-6 scale clamp): off ties their dequantised values agree to the
+    last bit or two of the product of the two scales."""
+    from oracle import nvfp4_sim as S
+    x = O.synthetic_tensor(64, 256, 77, outliers=False).float()
+    sim = S.quantize_1d(x)
+    real = O.dequant(O.quant_nvfp4(x.to(torch.bfloat16)))
+    assert (~torch.isclose(sim, real, rtol=1e-6, atol=0)).float().mean().item() < 5e-3

@@ -72,7 +72,7 @@ def test_backward_values_maxima_and_hints(Q):
     assert torch.allclose(du.float(), ru, rtol=2.0 ** -6, atol=1e-5)
     # the hints registered for the two gradients are the maxima of the stored gradients
     for t in (dg, du):
-        plain, rht = linear._take_grad_amax(t.reshape(-1, t.shape[-1]))
+        plain, rht = linear._take_grad_amax(t.reshape(-1, t.shape[-1]), signs)
         assert torch.equal(_bits(plain), _bits(quant.tensor_amax(t)))
         assert torch.equal(_bits(rht), _bits(quant.tensor_amax(t, rht=True, signs=signs, transpose=True)))
     assert linear._take_grad_amax(dg)[0] is None            # taken once
@@ -153,7 +153,7 @@ def test_relu2_values_maxima_and_hint(Q, shape):
     assert torch.equal(a, (torch.relu(xf) ** 2).to(torch.bfloat16))                 # one rounding of an exact product
     assert torch.equal(dx, (2 * torch.relu(xf) * d.float()).to(torch.bfloat16))
     assert torch.equal(_bits(mx[0:1]), _bits(quant.tensor_amax(a)))
-    plain, rht = linear._take_grad_amax(dx.reshape(-1, dx.shape[-1]))
+    plain, rht = linear._take_grad_amax(dx.reshape(-1, dx.shape[-1]), signs)
     assert torch.equal(_bits(plain), _bits(quant.tensor_amax(dx)))
     if has_rht:
         assert torch.equal(_bits(mx[1:2]), _bits(quant.tensor_amax(a, rht=True, signs=signs, transpose=True)))
@@ -186,3 +186,31 @@ def test_decoder_block_fused_activation_matches_torch_ops(Q):
     rel = lambda p, q: ((p.float() - q.float()).norm() / (q.float().norm() + 1e-30)).item()
     assert rel(ya, yb) < 2e-2
     assert all(rel(p, q) < 0.15 for p, q in zip(ga, gb))
+
+
+def test_hadamard_hint_is_dropped_for_another_sign_vector(Q):
+    """A maximum taken after the Hadamard transform belongs to the sign vector it was computed with:
+    a consumer that holds other signs gets the plain maximum only and recomputes the other; an equal
+    vector in another buffer is accepted (compared once, then remembered)."""
+    from nvfp4_sm120_b200 import linear
+    from oracle import nvfp4_oracle as O
+    g = torch.randn(64, 32, device="cuda").to(torch.bfloat16)
+    mx = torch.tensor([1.0, 2.0], device="cuda")
+    s3, s1 = O.signs_from_seed(3).cuda(), O.signs_from_seed(1).cuda()
+    linear.hint_grad_amax(g, mx, True, s3)
+    plain, rht = linear._take_grad_amax(g, s1)
+    assert plain is not None and rht is None
+    linear.hint_grad_amax(g, mx, True, s3)
+    plain, rht = linear._take_grad_amax(g, s3.clone())
+    assert plain is not None and rht is not None
+    lin = Q.FP4Linear(32, 16)
+    x = torch.randn(64, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    from nvfp4_sm120_b200 import quant
+    amax = torch.stack([quant.tensor_amax(x.detach())[0], torch.zeros((), device="cuda")])      # a WRONG Hadamard maximum
+    y1 = lin(x, amax=amax, amax_signs=s3)            # s3 is not the layer's vector: the wrong word is ignored
+    y1.sum().backward()
+    g1 = lin.weight.grad.clone()
+    lin.weight.grad = None
+    x.grad = None
+    lin(x).sum().backward()
+    assert torch.equal(lin.weight.grad, g1)
