@@ -1,0 +1,45 @@
+"""Loss parity with the reference recipe on the reference's own convergence task.
+
+The addition task of nvfp4_validate.py:239-282 / nvfp4_train.py:159-185 (same model, data split,
+optimizer and schedule) is trained three ways from the same seed:
+  * real FP4: every block linear an FP4Linear on the sm_100a kernels (hp_tail 0),
+  * reference recipe: the same model with the reference's fake-quant simulator
+    (`_NVFP4LinearFn`, nvfp4_validate.py:104-140, restated in oracle/nvfp4_sim.py and pinned to
+    golden vectors) in place of the FP4 linears, run with torch ops on the GPU,
+  * bf16.
+Held-out loss is compared at matched steps; the bound is the benchmark's: |difference| <= 0.02.
+The runs draw different stochastic-rounding streams (hardware dither against torch.rand), so the
+bound covers that noise too."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+STEPS, EVERY = 200, 50
+TOL = 0.02
+
+
+def test_fp4_loss_tracks_the_reference_recipe_and_bf16():
+    import nvfp4_sm120_b200 as Q
+    from nvfp4_sm120_b200 import addition
+    from oracle import nvfp4_sim as S
+
+    Q.set_amortize(True)
+    try:
+        quiet = lambda *_: None
+        fp4 = addition.run("fp4-all", STEPS, use_fp4=True, hp_tail=0, log=quiet, eval_every=EVERY)
+        sim = addition.run("reference-recipe", STEPS, use_fp4=True, hp_tail=0, log=quiet, eval_every=EVERY,
+                           linear_factory=lambda cin, cout: S.SimLinear(cin, cout, sr=True, rht=True, device="cuda"))
+        bf16 = addition.run("bf16", STEPS, use_fp4=False, log=quiet, eval_every=EVERY)
+    finally:
+        Q.set_amortize(False)
+    assert not fp4["diverged"] and not sim["diverged"] and not bf16["diverged"]
+    assert [h["step"] for h in fp4["history"]] == [h["step"] for h in sim["history"]] == list(range(EVERY, STEPS + 1, EVERY))
+    rows = []
+    for a, b, c in zip(fp4["history"], sim["history"], bf16["history"]):
+        rows.append((a["step"], a["val"], b["val"], c["val"]))
+    print("step, val loss real FP4 / reference recipe / bf16:", rows)
+    for step, v_fp4, v_sim, v_bf16 in rows:
+        assert abs(v_fp4 - v_sim) <= TOL, (step, v_fp4, v_sim)
+        assert abs(v_fp4 - v_bf16) <= 2 * TOL, (step, v_fp4, v_bf16)
+    assert Q.gemm_status() == 0
