@@ -392,7 +392,12 @@ int launch(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int 
 static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
                         const float* signs16, uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
                         float* pts_out, void* workspace, const float* amax_in, cudaStream_t stream) {
-  static const bool use_tiled = []() { const char* e = getenv("NVFP4_QUANT_TILED"); return e == nullptr || atoi(e) != 0; }();
+  // Kernel choice.  With the maximum given, the tile-form kernel (quantize_tiled.cu) is the faster one
+  // (15.9 / 20.5 / 23.7 us against 19.8 / 22.2 / 24.6 us at 8192 x 4096 in the three modes); for the
+  // two-phase launch the range-form kernel below is (26.6 / 30.1 / 35.5 us against 26.4 / 31.6 / 37.3).
+  // NVFP4_QUANT_TILED = 0 / 1 forces one of them for both cases (measurements, tests).
+  static const int force_tiled = []() { const char* e = getenv("NVFP4_QUANT_TILED"); return e == nullptr ? -1 : atoi(e); }();
+  const bool use_tiled = force_tiled < 0 ? amax_in != nullptr : force_tiled != 0;
   if (use_tiled)
     return nvfp4::tiled::launch(x, rows, cols, ld, mode, rht, signs16, seed, offset, qdata, scales, pts_out, workspace,
                                 amax_in, g_wait_ns.load(std::memory_order_relaxed),

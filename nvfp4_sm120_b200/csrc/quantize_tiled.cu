@@ -37,10 +37,11 @@ constexpr int kHalfThreads = 512;
 constexpr int kTileRows = 128;
 constexpr int kTileCols = 64;                              // elements: four blocks of 16
 constexpr int kTileBytes = kTileRows * kTileCols * 2;      // 16 KiB
-constexpr int kSlots = 5;                                  // ring depth per half CTA
-constexpr int kTabTiles = 32;                              // per half CTA: block maxima of its first 32 tiles
-constexpr int kRingBytes = 2 * kSlots * kTileBytes;        // 160 KiB
-constexpr int kTabBytes = 2 * kTabTiles * kHalfThreads * 2;   // 64 KiB
+constexpr int kPairBytes = 2 * kTileBytes;                 // a ring slot holds two consecutive tiles
+constexpr int kSlots = 3;                                  // ring depth per half CTA, in pairs
+constexpr int kTabTiles = 16;                              // per half CTA: block maxima of its first 16 tiles
+constexpr int kRingBytes = 2 * kSlots * kPairBytes;        // 192 KiB
+constexpr int kTabBytes = 2 * kTabTiles * kHalfThreads * 2;   // 32 KiB
 constexpr int kMiscOff = kRingBytes + kTabBytes;
 constexpr int kSmemBytes = kMiscOff + 1024 /* tables, barriers */ + 1024 /* alignment slack */;
 
@@ -82,6 +83,39 @@ __device__ __forceinline__ bool wait_phase(uint32_t bar, uint32_t parity, volati
   }
 }
 
+// Where this lane's block of the current tile goes: running pointers into the two outputs, the block's
+// Philox counter and whether the block lies inside the matrix.  step() moves to the next tile in range
+// order with additions only (a row of tiles ends every ntc tiles).
+struct Cursor {
+  uint8_t* q;            // this lane's 8 bytes of packed codes
+  uint8_t* s;            // this lane's scale byte
+  uint32_t i;            // block index row * bpr + k/16 (the Philox counter)
+  uint32_t ct, rt;
+  bool inside;
+};
+struct CursorConst {
+  uint32_t ntc, rows, bpr, row_t, kb;
+  uint64_t q_wrap;       // from the last tile of a row of tiles to the first of the next: 128 rows down, back to column 0
+  uint32_t i_wrap;
+};
+__device__ __forceinline__ void cursor_set(Cursor& c, const CursorConst& k, uint32_t tile, uint8_t* qdata, uint64_t q_pitch,
+                                           uint64_t q_lane, uint8_t* scales, uint32_t sc_lane) {
+  c.rt = tile / k.ntc;
+  c.ct = tile - c.rt * k.ntc;
+  c.q = qdata + (uint64_t)c.rt * (128u * q_pitch) + c.ct * 32u + q_lane;
+  c.s = scales + (uint64_t)tile * 512u + sc_lane;
+  c.i = (c.rt * 128u + k.row_t) * k.bpr + c.ct * 4u + k.kb;
+  c.inside = c.rt * 128u + k.row_t < k.rows && c.ct * 4u + k.kb < k.bpr;
+}
+__device__ __forceinline__ void cursor_step(Cursor& c, const CursorConst& k) {
+  c.q += 32; c.s += 512; c.i += 4u;
+  if (++c.ct == k.ntc) {
+    c.ct = 0; ++c.rt;
+    c.q += k.q_wrap; c.i += k.i_wrap;
+  }
+  c.inside = c.rt * 128u + k.row_t < k.rows && c.ct * 4u + k.kb < k.bpr;
+}
+
 template <bool SR, bool RHT, bool KNOWN>
 __global__ void __launch_bounds__(kThreads, 1)
 quant_tiled_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
@@ -91,27 +125,26 @@ quant_tiled_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   float* recip_tab = reinterpret_cast<float*>(smem + kMiscOff);          // 128 floats
   float* red = reinterpret_cast<float*>(smem + kMiscOff + 512);          // 32 floats
   float* sgs = reinterpret_cast<float*>(smem + kMiscOff + 640);          // 16 floats
-  const uint32_t bars = smem_u32(smem + kMiscOff + 704);                 // full[2][5], then empty[2][5]
-  volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + kMiscOff + 704 + 8 * 4 * kSlots);
+  const uint32_t bars = smem_u32(smem + kMiscOff + 704);                 // full[2][kSlots]: a pair has landed
+  const uint32_t counts = smem_u32(smem + kMiscOff + 704 + 8 * 2 * kSlots);   // done[2][kSlots]: warps finished with a slot
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(smem + kMiscOff + 704 + 8 * 2 * kSlots + 4 * 2 * kSlots);
 
   const uint32_t tid = threadIdx.x, half = tid >> 9, tih = tid & 511u, lane = tid & 31u, wsub = tih >> 5;
-  auto full_bar = [&](uint32_t s) { return bars + 8u * (half * kSlots + s); };
-  auto empty_bar = [&](uint32_t s) { return bars + 8u * (2 * kSlots + half * kSlots + s); };
-  const uint32_t ring = smem_u32(smem) + half * (kSlots * kTileBytes);
+  const uint32_t full0 = bars + 8u * (half * kSlots), done0 = counts + 4u * (half * kSlots);
+  const uint32_t ring = smem_u32(smem) + half * (kSlots * kPairBytes);
   uint16_t* tab = reinterpret_cast<uint16_t*>(smem + kRingBytes) + half * (kTabTiles * kHalfThreads) + tih;
 
-  // this half CTA's contiguous range of tiles
+  // this half CTA's contiguous range of tiles, walked in pairs
   const uint64_t halves = 2ull * gridDim.x, hid = 2ull * blockIdx.x + half;
   const uint32_t t0 = (uint32_t)(hid * p.ntiles / halves), t1 = (uint32_t)((hid + 1) * p.ntiles / halves);
-  const uint32_t nt = t1 - t0;
-  const uint32_t resident = KNOWN ? 0u : min(nt, (uint32_t)kSlots);      // tiles phase 1 leaves in the ring
-  const uint32_t head = nt - resident;                                   // tiles phase 2 fetches (again)
-  const bool elected = tih == 0;                                         // issues this half's copies
+  const uint32_t nt = t1 - t0, np = (nt + 1u) >> 1;
+  const uint32_t resident = KNOWN ? 0u : min(np, (uint32_t)kSlots);      // pairs phase 1 leaves in the ring
+  const uint32_t head = np - resident;                                   // pairs phase 2 fetches (again)
 
   if (tid == 0) {
     for (uint32_t b = 0; b < 2u * kSlots; ++b) {
       asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars + 8u * b));
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], 16;" ::"r"(bars + 8u * (2 * kSlots + b)));
+      asm volatile("st.shared.u32 [%0], %1;" ::"r"(counts + 4u * b), "r"(0u) : "memory");
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     *cta_abort = 0;
@@ -125,55 +158,63 @@ quant_tiled_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   __syncthreads();
 
   // ---- per-lane invariants ------------------------------------------------------------------
-  // lane -> (block kb of four, row pair h, row group g): rows {2 wsub + h + 32 g} of the tile
+  // lane -> (block kb of four, row pair h, row group g): rows {2 wsub + h + 32 g} of a tile
   const uint32_t kb = lane & 3u, hrow = (lane >> 2) & 1u, grp = lane >> 3;
   const uint32_t row_t = 2u * wsub + hrow + 32u * grp;
   const uint32_t off0 = row_t * 128u + (((2u * kb) ^ (row_t & 7u)) << 4);        // 128-byte swizzle: 16-byte chunk c
   const uint32_t off1 = row_t * 128u + (((2u * kb + 1u) ^ (row_t & 7u)) << 4);   // of row r sits at c ^ (r & 7)
   const uint32_t sc_lane = (2u * wsub + hrow) * 16u + grp * 4u + kb;             // byte inside the 512-byte scale tile
   const uint64_t q_lane = (uint64_t)row_t * p.q_pitch + kb * 8u;
-  const uint32_t i_lane = row_t * p.bpr + kb;                                    // block index inside a row of tiles
+  const CursorConst cc{p.ntc, p.rows, p.bpr, row_t, kb, 128ull * p.q_pitch - 32ull * p.ntc, 128u * p.bpr - 4u * p.ntc};
   uint32_t sm[8];                 // sign-bit masks of the packed bf16 pairs (bit 15: even, bit 31: odd)
 #pragma unroll
   for (int j = 0; j < 8; ++j)
     sm[j] = RHT ? ((sgs[2 * j] < 0.0f ? 0x8000u : 0u) | (sgs[2 * j + 1] < 0.0f ? 0x80000000u : 0u)) : 0u;
 
-  // fill f of this half's ring: tile t0 + f in phase 1 (f < nt), tile t0 + (f - nt) when phase 2 fetches
-  // the head of the range again; KNOWN has no phase 1, its fills are the tiles in order
+  // Fill number f of this half's ring goes to slot f % kSlots and completes phase (f / kSlots) & 1 of
+  // its barrier.  Phase 1 uses fills 0 .. np-1 (pair f of the range); phase 2 fetches the head of the
+  // range again as fills np .. (pair f - np).  KNOWN has no phase 1: its fills are the pairs in order.
   auto issue_fill = [&](uint32_t f) {
-    const uint32_t t = t0 + ((KNOWN || f < nt) ? f : f - nt);
-    const uint32_t rt = t / p.ntc, ct = t - rt * p.ntc;
-    const uint32_t s = f % kSlots;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full_bar(s)), "r"((uint32_t)kTileBytes) : "memory");
-    tma_tile_load(ring + s * kTileBytes, &map_x, (int)(ct * kTileCols), (int)(rt * kTileRows), full_bar(s));
+    const uint32_t pair = (KNOWN || f < np) ? f : f - np;
+    const uint32_t ta = t0 + 2u * pair;
+    const bool two = ta + 1u < t1;
+    const uint32_t rt = ta / p.ntc, ct = ta - rt * p.ntc;
+    const uint32_t s = f % kSlots, bar = full0 + 8u * s, dst = ring + s * kPairBytes;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
+                 ::"r"(bar), "r"((uint32_t)(two ? kPairBytes : kTileBytes)) : "memory");
+    tma_tile_load(dst, &map_x, (int)(ct * kTileCols), (int)(rt * kTileRows), bar);
+    if (two) {
+      const bool wrap = ct + 1u == p.ntc;
+      tma_tile_load(dst + kTileBytes, &map_x, (int)(wrap ? 0u : (ct + 1u) * kTileCols),
+                    (int)((wrap ? rt + 1u : rt) * kTileRows), bar);
+    }
   };
-  auto load_block = [&](uint32_t s, uint32_t (&w)[8]) {
-    uint4 a, b;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "r"(ring + s * kTileBytes + off0));
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "r"(ring + s * kTileBytes + off1));
-    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+  auto load_block = [&](uint32_t addr, uint32_t (&w)[8]) {
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr + off0));
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(addr + off1));
   };
-  // the slot has been read by this warp: one arrival per warp on its "empty" barrier
-  auto release_slot = [&](uint32_t s) {
+  // This warp has read slot s.  The warp that finishes LAST with the slot (sixteen share it) puts
+  // fill `next_f` into it; nobody waits for a slot to become free.  The acq_rel increment orders
+  // every warp's reads of the slot before the last one's copy into it.
+  auto release_and_refill = [&](uint32_t s, uint32_t next_f) {
     __syncwarp();
-    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(s)) : "memory");
-  };
-  uint32_t empty_waits = 0;       // elected thread: parity of its next wait on each slot's empty barrier (bit s)
-  auto refill_when_free = [&](uint32_t s, uint32_t f) -> bool {       // elected thread only
-    const bool ok = wait_phase(empty_bar(s), (empty_waits >> s) & 1u, cta_abort, p.wait_limit_ns);
-    empty_waits ^= 1u << s;
-    if (!ok) return false;
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic reads of the slot before the async write
-    issue_fill(f);
-    return true;
+    if (lane == 0) {
+      uint32_t before;
+      asm volatile("atom.acq_rel.cta.shared::cta.add.u32 %0, [%1], 1;" : "=r"(before) : "r"(done0 + 4u * s) : "memory");
+      if (before == 15u) {
+        asm volatile("st.shared.u32 [%0], %1;" ::"r"(done0 + 4u * s), "r"(0u) : "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // generic reads of the slot before the async write
+        issue_fill(next_f);
+      }
+    }
   };
   auto fail = [&](int code) {
     *cta_abort = 1;
     if (p.ws != nullptr) p.ws->error = code;
   };
 
-  if (elected) {
-    const uint32_t n0 = min(nt, (uint32_t)kSlots);
+  if (tih == 0) {
+    const uint32_t n0 = min(np, (uint32_t)kSlots);
     for (uint32_t f = 0; f < n0; ++f) issue_fill(f);
   }
 
@@ -181,28 +222,34 @@ quant_tiled_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   float amax;
   if (!KNOWN) {
     float m = 0.0f;
-    for (uint32_t c = 0; c < nt; ++c) {
-      const uint32_t s = c % kSlots;
-      if (!wait_phase(full_bar(s), (c / kSlots) & 1u, cta_abort, p.wait_limit_ns)) { fail(kErrCopy); break; }
-      uint32_t w[8];
-      load_block(s, w);
-      float a;
-      if (RHT) {
-        float v[16];
-        expand<true>(w, sm, v);
-        a = 0.0f;
+    uint32_t s = 0, par = 0;
+    uint16_t* tp = tab;                              // this lane's slot in the table of block maxima
+    for (uint32_t c = 0; c < np; ++c) {
+      if (!wait_phase(full0 + 8u * s, par, cta_abort, p.wait_limit_ns)) { fail(kErrCopy); break; }
+      uint32_t w[2][8];
+      const uint32_t addr = ring + s * kPairBytes;
+      load_block(addr, w[0]);
+      load_block(addr + kTileBytes, w[1]);               // the unused half of a last odd pair holds stale bytes
+      const bool two = 2u * c + 1u < nt;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(v[j]));
-        a *= 0.25f;
-      } else {
-        a = amax_packed8(w);
-        if (c < (uint32_t)kTabTiles) tab[c * kHalfThreads] = (uint16_t)(__float_as_uint(a) >> 16);
+      for (int e = 0; e < 2; ++e) {
+        float a;
+        if (RHT) {
+          float v[16];
+          expand<true>(w[e], sm, v);
+          a = 0.0f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) a = fmaxf(a, fabsf(v[j]));
+          a *= 0.25f;
+        } else {
+          a = amax_packed8(w[e]);
+          if (c < (uint32_t)(kTabTiles / 2)) tp[e * kHalfThreads] = (uint16_t)(__float_as_uint(a) >> 16);
+        }
+        if (e == 0 || two) m = fmaxf(m, a);
       }
-      m = fmaxf(m, a);
-      if (c + kSlots < nt) {                       // not one of the last five: the slot takes tile c + 5
-        release_slot(s);
-        if (elected && !refill_when_free(s, c + kSlots)) { fail(kErrCopy); break; }
-      }
+      tp += 2 * kHalfThreads;
+      if (c + kSlots < np) release_and_refill(s, c + kSlots);      // not one of the last pairs: the slot takes pair c + kSlots
+      if (++s == kSlots) { s = 0; par ^= 1u; }
     }
     if (stamper) p.ws->after[0] = (unsigned int)(global_ns() - t_start);
     m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 16));
@@ -265,76 +312,80 @@ quant_tiled_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   if (tid < 128) recip_tab[tid] = __fdiv_rn(sc.inv_pts, e4m3_to_f32(tid));
   __syncthreads();
 
-  // one tile: this lane's block (row row_t, block kb) of tile (rt, ct); k = position of the tile in
-  // the half's range (its block maximum is in the table when k < kTabTiles)
-  auto quantize_tile = [&](uint32_t s, uint32_t k, uint32_t rt, uint32_t ct) {
-    uint32_t w[8];
-    load_block(s, w);
-    float v[16];
-    float amax_b;
-    if (RHT) {
-      expand<true>(w, sm, v);
-      amax_b = 0.0f;
+  // One pair of tiles from a ring slot: this lane's block (row row_t, block kb) of each.  k = position
+  // of the pair's first tile in the half's range (block maxima of positions < kTabTiles are in the
+  // table at tp); cur = where the first tile's block goes, left at the tile after the pair.
+  auto quantize_pair = [&](uint32_t slot_addr, uint32_t k, const uint16_t* tp, Cursor& cur) {
+    uint32_t w[2][8];
+    load_block(slot_addr, w[0]);
+    load_block(slot_addr + kTileBytes, w[1]);
+    const bool two = k + 1u < nt;
 #pragma unroll
-      for (int j = 0; j < 16; ++j) amax_b = fmaxf(amax_b, fabsf(v[j]));
-      amax_b *= 0.25f;                                   // H = butterfly / 4, an exact scaling
-    } else {
-      expand<false>(w, sm, v);
-      amax_b = (!KNOWN && k < (uint32_t)kTabTiles) ? __uint_as_float((uint32_t)tab[k * kHalfThreads] << 16)
-                                                   : amax_packed8(w);
-    }
-    const uint32_t sf = block_scale_byte(amax_b, sc);
-    const float recip = RHT ? recip_tab[sf] * 0.25f : recip_tab[sf];
-    float d[16];
+    for (int e = 0; e < 2; ++e) {
+      if (e == 1 && !two) break;
+      float v[16];
+      float amax_b;
+      if (RHT) {
+        expand<true>(w[e], sm, v);
+        amax_b = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (RHT) mul2_poszero(v[2 * j], v[2 * j + 1], recip, d[2 * j], d[2 * j + 1]);
-      else mul2(v[2 * j], v[2 * j + 1], recip, d[2 * j], d[2 * j + 1]);
+        for (int j = 0; j < 16; ++j) amax_b = fmaxf(amax_b, fabsf(v[j]));
+        amax_b *= 0.25f;                                   // H = butterfly / 4, an exact scaling
+      } else {
+        expand<false>(w[e], sm, v);
+        amax_b = (!KNOWN && k < (uint32_t)kTabTiles) ? __uint_as_float((uint32_t)tp[e * kHalfThreads] << 16)
+                                                     : amax_packed8(w[e]);
+      }
+      const uint32_t sf = block_scale_byte(amax_b, sc);
+      const float recip = RHT ? recip_tab[sf] * 0.25f : recip_tab[sf];
+      float d[16];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (RHT) mul2_poszero(v[2 * j], v[2 * j + 1], recip, d[2 * j], d[2 * j + 1]);
+        else mul2(v[2 * j], v[2 * j + 1], recip, d[2 * j], d[2 * j + 1]);
+      }
+      uint32_t lo, hi;
+      if (SR) {
+        const Philox4 r = philox_rounds(cur.i, 0u, (uint32_t)p.offset, (uint32_t)(p.offset >> 32), p.keys);
+        lo = e2m1x4_rs(d[0], d[1], d[2], d[3], r.x) | (e2m1x4_rs(d[4], d[5], d[6], d[7], r.y) << 16);
+        hi = e2m1x4_rs(d[8], d[9], d[10], d[11], r.z) | (e2m1x4_rs(d[12], d[13], d[14], d[15], r.w) << 16);
+      } else {
+        lo = e2m1x8_rn(d);
+        hi = e2m1x8_rn(d + 8);
+      }
+      if (cur.inside) *reinterpret_cast<uint2*>(cur.q) = make_uint2(lo, hi);
+      // the scale tile is written whole: padding rows and columns read as zero
+      *cur.s = cur.inside ? (uint8_t)sf : (uint8_t)0;
+      cursor_step(cur, cc);
     }
-    const uint32_t row = rt * kTileRows + row_t, kbg = ct * 4u + kb;
-    const bool inside = row < p.rows && kbg < p.bpr;
-    uint32_t lo, hi;
-    if (SR) {
-      const uint32_t i = rt * (kTileRows * p.bpr) + ct * 4u + i_lane;       // = row * bpr + kbg
-      const Philox4 r = philox_rounds(i, 0u, (uint32_t)p.offset, (uint32_t)(p.offset >> 32), p.keys);
-      lo = e2m1x4_rs(d[0], d[1], d[2], d[3], r.x) | (e2m1x4_rs(d[4], d[5], d[6], d[7], r.y) << 16);
-      hi = e2m1x4_rs(d[8], d[9], d[10], d[11], r.z) | (e2m1x4_rs(d[12], d[13], d[14], d[15], r.w) << 16);
-    } else {
-      lo = e2m1x8_rn(d);
-      hi = e2m1x8_rn(d + 8);
-    }
-    if (inside)
-      *reinterpret_cast<uint2*>(p.qdata + (uint64_t)rt * (kTileRows * p.q_pitch) + ct * 32u + q_lane) = make_uint2(lo, hi);
-    // the scale tile is written whole: padding rows and columns read as zero
-    p.scales[(uint64_t)(rt * p.ntc + ct) * 512u + sc_lane] = inside ? (uint8_t)sf : (uint8_t)0;
   };
 
-  bool ok = true;
-  const uint32_t first_fetch = KNOWN ? 0u : nt;           // fill number of the first tile phase 2 fetches
-  // (a) the tiles phase 1 left in the ring, in range order; each freed slot takes the next head tile
-  for (uint32_t j = 0; j < resident && ok; ++j) {
-    const uint32_t k = head + j, f = k;                   // it arrived as fill k of phase 1
-    const uint32_t s = f % kSlots, t = t0 + k;
-    const uint32_t rt = t / p.ntc, ct = t - rt * p.ntc;
-    quantize_tile(s, k, rt, ct);
-    if (j < head) {                                       // head tile j comes next into this slot
-      release_slot(s);
-      if (elected && !refill_when_free(s, f + kSlots)) { fail(kErrCopy); ok = false; }
+  const uint32_t first_fetch = KNOWN ? 0u : np;           // fill number of the first pair phase 2 fetches
+  // (a) the pairs phase 1 left in the ring, in range order; each freed slot takes the next head pair
+  {
+    Cursor cur;
+    cursor_set(cur, cc, t0 + 2u * head, p.qdata, p.q_pitch, q_lane, p.scales, sc_lane);
+    const uint16_t* tp = tab + 2u * head * kHalfThreads;
+    for (uint32_t j = 0; j < resident; ++j) {
+      const uint32_t f = head + j, s = f % kSlots;          // it arrived as fill head + j of phase 1
+      quantize_pair(ring + s * kPairBytes, 2u * f, tp, cur);
+      tp += 2 * kHalfThreads;
+      if (j < head) release_and_refill(s, f + kSlots);      // head pair j comes next into this slot (np = head + kSlots)
     }
   }
   // (b) the head of the range, fetched (again) through the ring
   {
-    uint32_t rt = t0 / p.ntc, ct = t0 - rt * p.ntc;
-    for (uint32_t q = 0; q < head && ok; ++q) {
-      const uint32_t f = first_fetch + q, s = f % kSlots;
-      if (!wait_phase(full_bar(s), (f / kSlots) & 1u, cta_abort, p.wait_limit_ns)) { fail(kErrCopy); break; }
-      quantize_tile(s, q, rt, ct);
-      if (++ct == p.ntc) { ct = 0; ++rt; }
-      const uint32_t nq = KNOWN ? q + kSlots : q + resident;      // the head tile this slot takes next
-      if (nq < head) {
-        release_slot(s);
-        if (elected && !refill_when_free(s, first_fetch + nq)) { fail(kErrCopy); ok = false; }
-      }
+    Cursor cur;
+    cursor_set(cur, cc, t0, p.qdata, p.q_pitch, q_lane, p.scales, sc_lane);
+    const uint16_t* tp = tab;
+    uint32_t s = first_fetch % kSlots, par = (first_fetch / kSlots) & 1u;
+    for (uint32_t q = 0; q < head; ++q) {
+      if (!wait_phase(full0 + 8u * s, par, cta_abort, p.wait_limit_ns)) { fail(kErrCopy); break; }
+      quantize_pair(ring + s * kPairBytes, 2u * q, tp, cur);
+      tp += 2 * kHalfThreads;
+      const uint32_t nq = q + kSlots;                       // the head pair this slot takes next
+      if (nq < head) release_and_refill(s, first_fetch + nq);
+      if (++s == kSlots) { s = 0; par ^= 1u; }
     }
   }
   if (tid == 0 && p.ws != nullptr) {                               // diagnostics only, nothing waits for them

@@ -194,7 +194,7 @@ def test_hadamard_hint_is_dropped_for_another_sign_vector(Q):
     vector in another buffer is accepted (compared once, then remembered)."""
     from nvfp4_sm120_b200 import linear
     from oracle import nvfp4_oracle as O
-    g = torch.randn(64, 32, device="cuda").to(torch.bfloat16)
+    g = torch.randn(64, 64, device="cuda").to(torch.bfloat16)
     mx = torch.tensor([1.0, 2.0], device="cuda")
     s3, s1 = O.signs_from_seed(3).cuda(), O.signs_from_seed(1).cuda()
     linear.hint_grad_amax(g, mx, True, s3)
@@ -203,8 +203,8 @@ def test_hadamard_hint_is_dropped_for_another_sign_vector(Q):
     linear.hint_grad_amax(g, mx, True, s3)
     plain, rht = linear._take_grad_amax(g, s3.clone())
     assert plain is not None and rht is not None
-    lin = Q.FP4Linear(32, 16)
-    x = torch.randn(64, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    lin = Q.FP4Linear(64, 32)
+    x = torch.randn(64, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
     from nvfp4_sm120_b200 import quant
     amax = torch.stack([quant.tensor_amax(x.detach())[0], torch.zeros((), device="cuda")])      # a WRONG Hadamard maximum
     quant._SEED[0] = 77
