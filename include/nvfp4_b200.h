@@ -109,6 +109,24 @@ int nvfp4_quantize_fused_bf16(const void* x, int64_t rows, int64_t cols, int64_t
                               void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * Both quantized layouts of a weight w[rows, cols] (bf16, row stride ld) from ONE read, round to
+ * nearest, given the per-tensor amax word (nvfp4_amax_bf16, rht = 0):
+ *   qdata_rows / scales_rows   the [rows, cols] operand, blocks along cols  (fprop: quant(w))
+ *   qdata_cols / scales_cols   the [cols, rows] operand, blocks along rows  (dgrad: quant(w.t()))
+ * two_d == 0: every block has its own 1 x 16 scale: the bytes nvfp4_quantize_bf16 gives with
+ *             transpose = 0 and = 1.  Replaces the two weight quantizations of FP4Linear.forward
+ *             (nvfp4_train.py:72-78: quant(w) and quant(w.t().contiguous())).
+ * two_d != 0: one scale per 16 x 16 tile, used by the row-wise and the column-wise blocks that cross
+ *             it, so that both layouts dequantize to the same matrix -- the weight scaling of the
+ *             reference's simulator (quantize_nvfp4_2d, nvfp4_validate.py:68-82), here producing real
+ *             NVFP4 operands (the reference never ran this mode on FP4 hardware).
+ * Requirements: rows % 16 == 0, cols % 16 == 0, 16-byte aligned pointers, ld % 8 == 0.
+ */
+int nvfp4_quantize_weight_bf16(const void* w, int64_t rows, int64_t cols, int64_t ld, int two_d,
+                               const float* amax, uint8_t* qdata_rows, uint8_t* scales_rows,
+                               uint8_t* qdata_cols, uint8_t* scales_cols, float* pts_out, void* stream);
+
+/*
  * nvfp4_quantize_fused_bf16 for callers that cannot allocate device memory where they call from
  * (a C / FFI binding inside a runtime that gave all of HBM to its own pool, a callback that must
  * not hit cudaMalloc's implicit synchronisation): the kernel's scratch is a 256-byte device array

@@ -27,6 +27,9 @@ _SIGS = {
     "nvfp4_quantize_static_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
                                               _c.c_void_p, _c.c_uint64, _c.c_uint64, _c.c_void_p, _c.c_void_p,
                                               _c.c_void_p, _c.c_void_p]),
+    "nvfp4_quantize_weight_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_void_p,
+                                              _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                              _c.c_void_p]),
     "nvfp4_quantize_static_status": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p]),
     "nvfp4_swiglu_fwd_bf16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p,
                                          _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),

@@ -26,13 +26,19 @@ __device__ __forceinline__ GlobalScale global_scale(const float* __restrict__ am
 }
 
 // v[16] (already Hadamard-transformed if wanted) -> 8 bytes of codes (lo, hi) and the E4M3 byte.
-template <bool SR>
-__device__ __forceinline__ void encode_block(const float (&v)[16], const GlobalScale& g,
-                                             uint64_t blk_index, uint64_t seed, uint64_t offset,
-                                             uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
+__device__ __forceinline__ float block_amax16(const float (&v)[16]) {
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  return amax;
+}
+
+// amax: the maximum the block scale is derived from -- the block's own (1 x 16 scaling), or that of
+// the 16 x 16 tile around it (2-D weight scaling, nvfp4_validate.py:68-82)
+template <bool SR>
+__device__ __forceinline__ void encode_block_scaled(const float (&v)[16], float amax, const GlobalScale& g,
+                                                    uint64_t blk_index, uint64_t seed, uint64_t offset,
+                                                    uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
   const float bs = __fdiv_rn(amax, kF4Max);                                   // nvfp4_gemm.py:39
   const float sbs = fminf(fmaxf(__fdiv_rn(bs, g.pts), kE4M3Eps), kE4M3Max);   // :40
   sf_byte = f32_to_e4m3(sbs);
@@ -54,6 +60,13 @@ __device__ __forceinline__ void encode_block(const float (&v)[16], const GlobalS
     hi = e2m1x2_rn(v[8] * recip, v[9] * recip) | (e2m1x2_rn(v[10] * recip, v[11] * recip) << 8) |
          (e2m1x2_rn(v[12] * recip, v[13] * recip) << 16) | (e2m1x2_rn(v[14] * recip, v[15] * recip) << 24);
   }
+}
+
+template <bool SR>
+__device__ __forceinline__ void encode_block(const float (&v)[16], const GlobalScale& g,
+                                             uint64_t blk_index, uint64_t seed, uint64_t offset,
+                                             uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
+  encode_block_scaled<SR>(v, block_amax16(v), g, blk_index, seed, offset, lo, hi, sf_byte);
 }
 
 __device__ __forceinline__ void load_signs(const float* __restrict__ signs16, float (&sg)[16]) {
@@ -277,6 +290,81 @@ __global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restr
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// weights: both layouts from one read.  A CTA takes a 64 x 64 tile of w [rows, cols]; thread
+// (row t / 4, segment t % 4) loads the 16 elements of row-wise block (row, segment) and leaves them in
+// a padded shared tile, from which thread (column t % 64, row block t / 64) reads the 16 elements of
+// column-wise block (column, row block).  Round to nearest only (weights).  TWO_D: one scale per
+// 16 x 16 tile, shared by the row-wise and the column-wise blocks that cross it, so that both
+// quantized layouts hold the same values (the reference simulator's weight scaling,
+// nvfp4_validate.py:68-82); otherwise every block has its own 1 x 16 scale, as quant_nvfp4 gives.
+// ---------------------------------------------------------------------------------------
+template <bool TWO_D>
+__global__ void __launch_bounds__(256) quant_weight_dual_kernel(const uint16_t* __restrict__ w, int64_t rows, int64_t cols,
+                                                                int64_t ld, const float* __restrict__ amax,
+                                                                uint8_t* __restrict__ q_rows, uint8_t* __restrict__ sf_rows,
+                                                                uint8_t* __restrict__ q_cols, uint8_t* __restrict__ sf_cols,
+                                                                float* __restrict__ pts_out) {
+  __shared__ uint16_t tile[64][66];          // 33 words per row: a column walk touches 16 different banks
+  __shared__ float bmax[64][4];              // row-wise block maxima of the tile
+  __shared__ float tmax[4][4];               // 16 x 16 tile maxima
+  const GlobalScale g = global_scale(amax);
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
+  const int t = threadIdx.x;
+  const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
+  // ---- load: row-wise block (r, seg) ----
+  const int r = t >> 2, seg = t & 3;
+  const int64_t gr = r0 + r, gc = c0 + seg * 16;
+  const bool have = gr < rows && gc < cols;          // rows and cols are multiples of 16: a block is whole or absent
+  uint32_t wv[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+  if (have) {
+    const uint4* p = reinterpret_cast<const uint4*>(w + gr * ld + gc);
+    const uint4 a = __ldg(p), b = __ldg(p + 1);
+    wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+  }
+  float v[16];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    v[2 * j] = bf16_lo(wv[j]);
+    v[2 * j + 1] = bf16_hi(wv[j]);
+    *reinterpret_cast<uint32_t*>(&tile[r][seg * 16 + 2 * j]) = wv[j];
+  }
+  const float my_max = block_amax16(v);
+  if (TWO_D) bmax[r][seg] = my_max;
+  __syncthreads();
+  if (TWO_D) {
+    if (t < 16) {
+      const int rb = t >> 2, cb = t & 3;
+      float m = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m = fmaxf(m, bmax[rb * 16 + i][cb]);
+      tmax[rb][cb] = m;
+    }
+    __syncthreads();
+  }
+  // ---- row-wise output ----
+  if (have) {
+    uint32_t lo, hi, sf;
+    encode_block_scaled<false>(v, TWO_D ? tmax[r >> 4][seg] : my_max, g, 0, 0, 0, lo, hi, sf);
+    const int64_t kb = gc >> 4;
+    *reinterpret_cast<uint2*>(q_rows + gr * (cols >> 1) + kb * 8) = make_uint2(lo, hi);
+    sf_rows[sf_offset(gr, kb, ((cols >> 4) + 3) >> 2)] = (uint8_t)sf;
+  }
+  // ---- column-wise output: block (column c, row block rb) ----
+  const int c = t & 63, rb = t >> 6;
+  const int64_t oc = c0 + c, orow0 = r0 + rb * 16;
+  if (oc < cols && orow0 < rows) {
+    float u[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) u[i] = __uint_as_float((uint32_t)tile[rb * 16 + i][c] << 16);
+    uint32_t lo, hi, sf;
+    encode_block_scaled<false>(u, TWO_D ? tmax[rb][c >> 4] : block_amax16(u), g, 0, 0, 0, lo, hi, sf);
+    const int64_t kb = orow0 >> 4;
+    *reinterpret_cast<uint2*>(q_cols + oc * (rows >> 1) + kb * 8) = make_uint2(lo, hi);
+    sf_cols[sf_offset(oc, kb, ((rows >> 4) + 3) >> 2)] = (uint8_t)sf;
+  }
+}
+
 static inline int grid_for(int64_t work_items, int threads, int max_blocks) {
   int64_t b = (work_items + threads - 1) / threads;
   if (b > max_blocks) b = max_blocks;
@@ -373,5 +461,34 @@ extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, in
     else NVFP4_LAUNCH_COLS(false, false);
 #undef NVFP4_LAUNCH_COLS
   }
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+
+
+extern "C" int nvfp4_quantize_weight_bf16(const void* w, int64_t rows, int64_t cols, int64_t ld, int two_d,
+                                          const float* amax, uint8_t* qdata_rows, uint8_t* scales_rows,
+                                          uint8_t* qdata_cols, uint8_t* scales_cols, float* pts_out, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!w || !amax || !qdata_rows || !scales_rows || !qdata_cols || !scales_cols) return NVFP4_E_NULL;
+  if (rows <= 0 || cols <= 0 || ld < cols || (rows & 15) != 0 || (cols & 15) != 0) return NVFP4_E_SHAPE;
+  if (!aligned16(w) || (ld & 7) != 0 || !aligned16(qdata_rows) || !aligned16(qdata_cols) || !aligned16(scales_rows) ||
+      !aligned16(scales_cols))
+    return NVFP4_E_ALIGN;
+  // padding of the tiled scale buffers must read as zero
+  auto clear_if_padded = [&](uint8_t* sf, int64_t m, int64_t k) {
+    const int64_t sm = (m + 127) / 128 * 128, sk = (k / 16 + 3) / 4 * 4;
+    if (sm == m && sk == k / 16) return true;
+    return cudaMemsetAsync(sf, 0, (size_t)(sm * sk), stream) == cudaSuccess;
+  };
+  if (!clear_if_padded(scales_rows, rows, cols) || !clear_if_padded(scales_cols, cols, rows)) return NVFP4_E_LAUNCH;
+  const dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
+  if (grid.y > 65535u) return NVFP4_E_LIMIT;
+  const uint16_t* wp = static_cast<const uint16_t*>(w);
+  if (two_d)
+    quant_weight_dual_kernel<true><<<grid, 256, 0, stream>>>(wp, rows, cols, ld, amax, qdata_rows, scales_rows, qdata_cols,
+                                                             scales_cols, pts_out);
+  else
+    quant_weight_dual_kernel<false><<<grid, 256, 0, stream>>>(wp, rows, cols, ld, amax, qdata_rows, scales_rows, qdata_cols,
+                                                              scales_cols, pts_out);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }

@@ -20,7 +20,7 @@ import torch
 import torch.nn as nn
 
 from .gemm import nvfp4_mm
-from .quant import hadamard16, quant_nvfp4, tensor_amax
+from .quant import hadamard16, quant_nvfp4, quant_weight_nvfp4, tensor_amax
 from .tensor import BLK
 
 _STEP = [0]          # bumped once per optimizer step; the weight-quant cache keys on it
@@ -172,10 +172,11 @@ def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, tran
 
 class WeightQuantCache:
     """quant(w) and quant(w.t()) of one weight, recomputed when the global step moves
-    (nvfp4_train.py:72-78).  One amax pass serves both layouts."""
+    (nvfp4_train.py:72-78): one amax pass, then both layouts from one read of the weight.
+    two_d: 16 x 16 scaling tiles instead of 1 x 16 blocks (both layouts then hold the same values)."""
 
-    def __init__(self):
-        self.step, self.wq_K, self.wq_N = -1, None, None
+    def __init__(self, two_d=False):
+        self.step, self.wq_K, self.wq_N, self.two_d = -1, None, None, bool(two_d)
 
     def get(self, weight, amax_reduce=None):
         if not _AMORTIZE:
@@ -187,8 +188,8 @@ class WeightQuantCache:
             amax = tensor_amax(w)
             if amax_reduce is not None:
                 amax_reduce(amax)
-            self.wq_K = quant_nvfp4(w, amax=amax)                      # [N, K], contraction K (fprop)
-            self.wq_N = quant_nvfp4(w, amax=amax, transpose=True)      # [K, N], contraction N (dgrad)
+            # [N, K] with contraction K (fprop) and [K, N] with contraction N (dgrad)
+            self.wq_K, self.wq_N = quant_weight_nvfp4(w, amax=amax, two_d=self.two_d)
             self.step = _STEP[0]
         return self.wq_K, self.wq_N
 
@@ -196,15 +197,18 @@ class WeightQuantCache:
 class FP4Linear(nn.Module):
     """Drop-in for nn.Linear(cin, cout, bias=False) with fp32 master weights (nvfp4_train.py:58-80)."""
 
-    def __init__(self, cin, cout, device="cuda"):
+    def __init__(self, cin, cout, device="cuda", weight_scaling="1d"):
+        """weight_scaling: "1d" (1 x 16 blocks, the reference's real-FP4 path) or "2d" (16 x 16 tiles, its
+        simulator's weight scaling; takes effect on the cached path, NVFP4_AMORTIZE=1)."""
         super().__init__()
         assert cin % BLK == 0 and cout % BLK == 0
+        assert weight_scaling in ("1d", "2d")
         self.weight = nn.Parameter(torch.empty(cout, cin, device=device))
         nn.init.normal_(self.weight, std=0.02)
         self.register_buffer("H", hadamard16(device))
         g = torch.Generator().manual_seed(1)
         self.register_buffer("signs", (torch.randint(0, 2, (BLK,), generator=g).float() * 2 - 1).to(device))
-        self._cache = WeightQuantCache()
+        self._cache = WeightQuantCache(two_d=weight_scaling == "2d")
 
     # the reference's field names (nvfp4_train.py:67-68)
     @property

@@ -151,5 +151,34 @@ def quant_nvfp4(t, stochastic=False, rht=False, H=None, signs=None, seed=None, *
     return NVFP4Tensor(qdata, scale.view(torch.float8_e4m3fn), BLK, t.dtype, pts, True)
 
 
+def quant_weight_nvfp4(w, amax=None, two_d=False):
+    """(quant(w), quant(w.t())) of a weight [N, K] from one read of w, round to nearest: the two
+    operands FP4Linear needs (nvfp4_train.py:72-78).  two_d=True scales 16 x 16 tiles (the simulator's
+    weight scaling, nvfp4_validate.py:68-82), so that both layouts dequantize to the same matrix.
+    amax: optional 1-element fp32 CUDA tensor (a sharded weight passes the group-reduced maximum)."""
+    x = _as_bf16_rows(w)
+    rows, cols = x.shape
+    if rows % BLK != 0 or cols % BLK != 0:
+        raise AssertionError(f"weight dims {rows}x{cols} must be divisible by {BLK}")
+    dev = x.device
+    if amax is None:
+        amax = tensor_amax(x)
+    _lib.cuda_device_of(x, amax)
+    sm_r, sk_r = swizzled_scale_dims(rows, cols)
+    sm_c, sk_c = swizzled_scale_dims(cols, rows)
+    q_r = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+    s_r = torch.empty((sm_r, sk_r), dtype=torch.uint8, device=dev)
+    q_c = torch.empty((cols, rows // 2), dtype=torch.uint8, device=dev)
+    s_c = torch.empty((sm_c, sk_c), dtype=torch.uint8, device=dev)
+    pts = torch.empty((), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        code = _lib.lib().nvfp4_quantize_weight_bf16(x.data_ptr(), rows, cols, x.stride(0), int(two_d), amax.data_ptr(),
+                                                     q_r.data_ptr(), s_r.data_ptr(), q_c.data_ptr(), s_c.data_ptr(),
+                                                     pts.data_ptr(), _stream(dev))
+    _lib.check(code, "nvfp4_quantize_weight_bf16")
+    return (NVFP4Tensor(q_r, s_r.view(torch.float8_e4m3fn), BLK, w.dtype, pts, True),
+            NVFP4Tensor(q_c, s_c.view(torch.float8_e4m3fn), BLK, w.dtype, pts, True))
+
+
 # the reference's second name for the same entry (nvfp4_cuda.py:158)
 quant_nvfp4_cuda = quant_nvfp4

@@ -354,6 +354,31 @@ def quant_nvfp4(t: torch.Tensor, stochastic: bool = False, rht: bool = False,
                        scaled if keep_scaled else None)
 
 
+def quant_nvfp4_weight_2d(w: torch.Tensor) -> tuple[OracleNVFP4, OracleNVFP4]:
+    """Real NVFP4 operands with the simulator's 16 x 16 weight scaling (nvfp4_validate.py:68-82):
+    one E4M3 scale per 16 x 16 tile, derived like quant_nvfp4 derives a block scale (tile amax / 6,
+    divided by the per-tensor scale, clamped to [2^-6, 448]) and stored once per 1 x 16 block of each
+    layout.  Returns (quant of w [N, K] along K, quant of w.t() [K, N] along N); both dequantize to
+    the same matrix.  Round to nearest, ties to even."""
+    n, k = w.shape
+    assert n % BLK == 0 and k % BLK == 0
+    wf = w.float()
+    amax = wf.abs().amax().clamp_min(1e-12)
+    pts = amax / (F4_MAX * F8E4M3_MAX)
+    tiles = wf.reshape(n // BLK, BLK, k // BLK, BLK)
+    tile_scale = tiles.abs().amax(dim=(1, 3)) / F4_MAX                      # [N/16, K/16]
+    sbs = (tile_scale / pts).clamp(E4M3_EPS, F8E4M3_MAX).to(torch.float8_e4m3fn)
+    recip = (1.0 / pts) / sbs.float()
+    scaled = (tiles * recip[:, None, :, None]).reshape(n, k).clamp(-F4_MAX, F4_MAX)
+    codes = e2m1_encode_rne(scaled)
+    sb = sbs.view(torch.uint8)
+    srm_rows = sb.repeat_interleave(BLK, dim=0).contiguous()                # [N, K/16]
+    srm_cols = sb.t().repeat_interleave(BLK, dim=0).contiguous()            # [K, N/16]
+    rows = OracleNVFP4(pack_nibbles(codes), swizzle_scales(srm_rows), pts.reshape(()), (n, k), srm_rows)
+    cols = OracleNVFP4(pack_nibbles(codes.t().contiguous()), swizzle_scales(srm_cols), pts.reshape(()), (k, n), srm_cols)
+    return rows, cols
+
+
 def dequant(q: OracleNVFP4) -> torch.Tensor:
     """NVFP4 -> fp32 [M, K]: code value * E4M3 block scale * per-tensor scale."""
     m, k = q.shape

@@ -221,3 +221,17 @@ def test_simulator_tracks_the_real_fp4_recipe():
     sim = S.quantize_1d(x)
     real = O.dequant(O.quant_nvfp4(x.to(torch.bfloat16)))
     assert (~torch.isclose(sim, real, rtol=1e-6, atol=0)).float().mean().item() < 5e-3
+
+
+def test_weight_2d_scaling_oracle(golden):
+    """The real-NVFP4 form of the simulator's 16 x 16 weight scaling: both layouts dequantize to the
+    same matrix, which equals the simulator's fake-quant off ties (tie direction and the scale clamp
+    are the documented differences)."""
+    from oracle import nvfp4_sim as S
+    w = golden["sim.w"]
+    qr, qc = O.quant_nvfp4_weight_2d(w)
+    assert torch.equal(O.dequant(qr), O.dequant(qc).t())
+    sim = golden["sim.w2d"]
+    assert (~torch.isclose(O.dequant(qr), sim, rtol=1e-6, atol=0)).float().mean().item() < 5e-3
+    # a tile's sixteen row blocks carry the same scale byte
+    assert torch.equal(qr.scale_rowmajor.reshape(3, 16, 4)[:, 0], qr.scale_rowmajor.reshape(3, 16, 4)[:, 15])
