@@ -175,6 +175,23 @@ int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
                int32_t* status, void* stream);
 
 /*
+ * The same GEMM with an NVFP4 OUTPUT for chained GEMMs: every output row is rounded to bf16 and
+ * quantized in blocks of 16 along N (round to nearest) inside the epilogue, with the per-tensor
+ * maximum *d_amax supplied by the caller (a value known from the previous step or a bound; elements
+ * beyond it saturate).  Outputs: d_q [M, N/2] packed E2M1, d_sf the swizzled E4M3 scales of the
+ * [M, N] operand, *d_pts = max(*d_amax, 1e-12) / 2688 -- exactly what nvfp4_quantize_bf16 would make
+ * of the bf16 output of nvfp4_gemm with the same amax word, without that tensor ever reaching
+ * memory.  Requirements of nvfp4_gemm, and N % 16 == 0.
+ * Counterpart in the reference: the E2M1 output + scale-factor epilogue of its CUTLASS example
+ * (cutlass_gemm/nvfp4_gemm.cu:106-108, :149-154: LinCombBlockScaleFactor), which takes the
+ * normalisation constant from the caller in the same way.
+ */
+int nvfp4_gemm_fp4out(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
+                      const uint8_t* b_q, const uint8_t* b_sf, const float* b_pts,
+                      int64_t M, int64_t N, int64_t K, const float* d_amax,
+                      uint8_t* d_q, uint8_t* d_sf, float* d_pts, int32_t* status, void* stream);
+
+/*
  * Kernel choice of nvfp4_gemm for this process: 0 = automatic (the default), 1 = always the
  * one-CTA 128x256 kernel, 2 = always the persistent two-CTA 256x256 kernel.  For tuning and tests;
  * results are the same to rounding of the accumulation order.  No counterpart in the reference.

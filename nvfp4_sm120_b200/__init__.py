@@ -6,6 +6,6 @@ C ABI of libnvfp4_b200.so."""
 from .tensor import NVFP4Tensor, BLK, swizzled_scale_dims            # noqa: F401
 from .quant import (quant_nvfp4, quant_nvfp4_cuda, quant_weight_nvfp4, tensor_amax, hadamard16,      # noqa: F401
                     F4_MAX, F8E4M3_MAX, E4M3_EPS)
-from .gemm import nvfp4_mm, fp4_matmul, fp4_matmul_cuda, fp4_mm_preqB, gemm_status      # noqa: F401
+from .gemm import nvfp4_mm, nvfp4_mm_fp4out, fp4_matmul, fp4_matmul_cuda, fp4_mm_preqB, gemm_status      # noqa: F401
 from .linear import FP4Linear, FP4LinearFn, mark_step, make_linear, set_amortize      # noqa: F401
 from . import linear      # noqa: F401

@@ -31,11 +31,22 @@ extern "C" int nvfp4_gemm_set_mode(int mode) {
 // Automatic choice: the persistent pair kernel (mode 2), which measured fastest on every shape with
 // more than one row tile; the one-CTA kernel (mode 1) when M <= 128 (a pair would compute 128 rows of
 // padding) and for the split-K case below.  Modes 1 and 2 force a kernel, for tuning and tests.
-extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
-                          const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
-                          int64_t K, int64_t ldd, int32_t* status, void* stream_) {
+namespace nvfp4 { namespace gemm {
+__global__ void pts_from_amax_kernel(const float* __restrict__ amax, float* __restrict__ pts) {
+  *pts = __fdiv_rn(fmaxf(*amax, kAmaxFloor), kGlobalDiv);
+}
+int launch_pts_from_amax(const float* amax, float* pts, cudaStream_t stream) {
+  pts_from_amax_kernel<<<1, 1, 0, stream>>>(amax, pts);
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+}}
+
+static int gemm_any(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
+                    const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
+                    int64_t K, int64_t ldd, uint8_t* d_sf, const float* d_amax, int32_t* status, void* stream_) {
   using namespace nvfp4::gemm;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const bool fp4_out = d_sf != nullptr;
   if (!a_q || !a_sf || !a_pts || !b_q || !b_sf || !b_pts || !d) return NVFP4_E_NULL;
   if (M <= 0 || N <= 0 || K <= 0 || (K & 31) != 0 || ldd < N) return NVFP4_E_SHAPE;
   if (M > 0x7fffffffLL || N > 0x7fffffffLL || K > 0x7fffffffLL) return NVFP4_E_SHAPE;
@@ -52,7 +63,8 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
   if (!make_operand_map(&map_a, a_q, M, K, 128) || !make_operand_map(&map_b, b_q, N, K, pair ? 128 : 256))
     return NVFP4_E_DRIVER;
   Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status, 1, 0,
-           g_gemm_wait_ns.load(std::memory_order_relaxed), g_gemm_drop_arrival.load(std::memory_order_relaxed)};
+           g_gemm_wait_ns.load(std::memory_order_relaxed), g_gemm_drop_arrival.load(std::memory_order_relaxed),
+           d_sf, d_amax, fp4_out ? 1 : 0};
   // Split K when a small fp32 output (the weight gradient: few tiles, K = tokens) would leave most SMs
   // idle: the CTAs of a tile add their partial sums into the zeroed output.  Summation order then
   // varies from run to run in the last bits, so it is used only where it pays: fewer tiles than half
@@ -72,9 +84,31 @@ extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* 
   // The epilogue stores through TMA when the row pitch allows a tensor map (a multiple of 16 bytes)
   // and the output is written, not accumulated into.
   CUtensorMap map_d = map_a;                                   // placeholder when unused
-  if (p.splits == 1 && (ldd * (p.out_f32 ? 4 : 2)) % 16 == 0) {
+  if (p.splits == 1 && !fp4_out && (ldd * (p.out_f32 ? 4 : 2)) % 16 == 0) {
     if (!make_output_map(&map_d, d, M, N, ldd, p.out_f32 != 0)) return NVFP4_E_DRIVER;
     p.tma_store = 1;
   }
   return pair ? nvfp4::gemm3::launch_pair(map_a, map_b, map_d, p, stream) : launch_1cta(map_a, map_b, map_d, p, stream);
+}
+
+extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
+                          const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
+                          int64_t K, int64_t ldd, int32_t* status, void* stream_) {
+  return gemm_any(a_q, a_sf, a_pts, b_q, b_sf, b_pts, d, out_dtype, M, N, K, ldd, nullptr, nullptr, status, stream_);
+}
+
+extern "C" int nvfp4_gemm_fp4out(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
+                                 const uint8_t* b_sf, const float* b_pts, int64_t M, int64_t N, int64_t K,
+                                 const float* d_amax, uint8_t* d_q, uint8_t* d_sf, float* d_pts, int32_t* status,
+                                 void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!d_amax || !d_q || !d_sf || !d_pts) return NVFP4_E_NULL;
+  if ((N & 15) != 0) return NVFP4_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(d_sf) & 15u) != 0) return NVFP4_E_ALIGN;
+  // padding of the tiled scale buffer reads as zero; the per-tensor scale is the given maximum / 2688
+  const int64_t sm = (M + 127) / 128 * 128, sk = (N / 16 + 3) / 4 * 4;
+  if ((sm != M || sk != N / 16) && cudaMemsetAsync(d_sf, 0, (size_t)(sm * sk), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
+  const int rc = gemm_any(a_q, a_sf, a_pts, b_q, b_sf, b_pts, d_q, NVFP4_OUT_BF16, M, N, K, N, d_sf, d_amax, status, stream_);
+  if (rc != NVFP4_OK) return rc;
+  return nvfp4::gemm::launch_pts_from_amax(d_amax, d_pts, stream);
 }

@@ -148,6 +148,11 @@ struct Params {
   unsigned long long wait_limit_ns;   // every bounded wait gives up after this long (0 = kWaitLimitNs)
   int drop_first_scale_arrival;       // test hook: the scale warps never announce K slice 0, so the MMA
                                       // issuer's first wait runs out and the kernel takes its abort path
+  // NVFP4 output (out_fp4 != 0): d is the packed E2M1 buffer [M, N/2]; the bf16 rounding of every
+  // output row is quantized in blocks of 16 along N with the per-tensor maximum *d_amax given
+  uint8_t* d_sf;                      // swizzled E4M3 scales of the [M, N] operand
+  const float* d_amax;
+  int out_fp4;
 };
 
 __device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status, int code) {
@@ -158,9 +163,48 @@ __device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status,
 
 // 32 consecutive accumulator columns of one output row: scale by alpha, convert, store
 // (vector stores when the chunk is whole and the leading dimension allows it).
+// 16 consecutive values of one output row -> 8 bytes of E2M1 codes and the block's E4M3 scale byte, with
+// the quantizer's own operations (nvfp4_gemm.py:36-45: true divisions, clamp, RNE) applied to the bf16
+// rounding of the values, i.e. what quantizing the stored bf16 output with this maximum would give.
+__device__ __forceinline__ void quantize_out_block(const uint32_t* acc, float alpha, float pts, float inv_pts,
+                                                   uint32_t& lo, uint32_t& hi, uint32_t& sf) {
+  float v[16];
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    v[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(acc[j]) * alpha));
+    amax = fmaxf(amax, fabsf(v[j]));
+  }
+  const float sbs = fminf(fmaxf(__fdiv_rn(__fdiv_rn(amax, kF4Max), pts), kE4M3Eps), kE4M3Max);
+  sf = f32_to_e4m3(sbs);
+  const float recip = __fdiv_rn(inv_pts, e4m3_to_f32(sf));
+  lo = e2m1x2_rn(v[0] * recip, v[1] * recip) | (e2m1x2_rn(v[2] * recip, v[3] * recip) << 8) |
+       (e2m1x2_rn(v[4] * recip, v[5] * recip) << 16) | (e2m1x2_rn(v[6] * recip, v[7] * recip) << 24);
+  hi = e2m1x2_rn(v[8] * recip, v[9] * recip) | (e2m1x2_rn(v[10] * recip, v[11] * recip) << 8) |
+       (e2m1x2_rn(v[12] * recip, v[13] * recip) << 16) | (e2m1x2_rn(v[14] * recip, v[15] * recip) << 24);
+}
+
 __device__ __forceinline__ void store_row_chunk(const Params& p, int64_t row, int64_t col, const uint32_t (&r)[32],
                                                 float alpha) {
   const bool full = (col + 32 <= p.N);
+  if (p.out_fp4) {                                      // N is a multiple of 16: a block is whole or absent
+    const float pts = __fdiv_rn(fmaxf(__ldg(p.d_amax), kAmaxFloor), kGlobalDiv);
+    const float inv_pts = __fdiv_rn(1.0f, pts);
+    uint8_t* q = static_cast<uint8_t*>(p.d) + row * (p.N >> 1) + (col >> 1);
+    const int64_t col_tiles = ((p.N >> 4) + 3) >> 2;
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+    for (int b = 0; b < 2; ++b) {
+      if (col + 16 * b < p.N) {
+        uint32_t sf;
+        quantize_out_block(&r[16 * b], alpha, pts, inv_pts, w[2 * b], w[2 * b + 1], sf);
+        p.d_sf[sf_offset(row, (col >> 4) + b, col_tiles)] = (uint8_t)sf;
+      }
+    }
+    if (full) *reinterpret_cast<uint4*>(q) = make_uint4(w[0], w[1], w[2], w[3]);
+    else *reinterpret_cast<uint2*>(q) = make_uint2(w[0], w[1]);
+    return;
+  }
   if (p.splits > 1) {                                   // split-K partial sum (fp32 output only)
     float* out = static_cast<float*>(p.d) + row * p.ldd + col;
     if (full && ((p.ldd & 3) == 0)) {                   // four floats per reduction instruction

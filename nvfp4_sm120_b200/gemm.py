@@ -56,6 +56,35 @@ def nvfp4_mm(a: NVFP4Tensor, b: NVFP4Tensor, out_dtype=None, out=None) -> torch.
     return d
 
 
+def nvfp4_mm_fp4out(a: NVFP4Tensor, b: NVFP4Tensor, out_amax: torch.Tensor) -> NVFP4Tensor:
+    """a @ b delivered as an NVFP4Tensor [M, N] quantized along N (round to nearest) inside the GEMM
+    epilogue, for a GEMM that feeds another one: equal to quant_nvfp4(nvfp4_mm(a, b, bfloat16),
+    amax=out_amax) without the bf16 tensor in memory.  out_amax: 1-element fp32 CUDA tensor, the
+    per-tensor maximum to scale with (known from an earlier step, or a bound: larger values saturate)."""
+    from .tensor import BLK, swizzled_scale_dims
+    if a._transposed or not b._transposed:
+        raise ValueError("nvfp4_mm_fp4out expects a = quant(A) and b = quant(B.t()).t()")
+    m, k2 = a.qdata.shape
+    n, k2b = b.qdata.shape
+    if k2 != k2b:
+        raise ValueError(f"contraction mismatch: {k2 * 2} vs {k2b * 2}")
+    if n % BLK != 0:
+        raise AssertionError(f"N={n} must be divisible by {BLK}")
+    dev = _lib.cuda_device_of(a.qdata, a.scale, a.per_tensor_scale, b.qdata, b.scale, b.per_tensor_scale, out_amax)
+    sm, sk = swizzled_scale_dims(m, n)
+    qd = torch.empty((m, n // 2), dtype=torch.uint8, device=dev)
+    sc = torch.empty((sm, sk), dtype=torch.uint8, device=dev)
+    pts = torch.empty((), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        code = _lib.lib().nvfp4_gemm_fp4out(
+            a.qdata.data_ptr(), a.scale.data_ptr(), a.per_tensor_scale.data_ptr(),
+            b.qdata.data_ptr(), b.scale.data_ptr(), b.per_tensor_scale.data_ptr(),
+            m, n, k2 * 2, out_amax.data_ptr(), qd.data_ptr(), sc.data_ptr(), pts.data_ptr(),
+            _status_word(dev).data_ptr(), _stream(dev))
+    _lib.check(code, "nvfp4_gemm_fp4out")
+    return NVFP4Tensor(qd, sc.view(torch.float8_e4m3fn), BLK, torch.bfloat16, pts, True)
+
+
 def _quant_rhs(B, stochastic, rht, H, signs, seed):
     """quant(B.t()) for B [K, N] without materialising the transpose."""
     if B.stride(0) == 1 and B.dim() == 2:           # B is itself a transposed view: B.t() is row-major

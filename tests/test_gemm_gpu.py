@@ -192,3 +192,34 @@ def test_standalone_c_driver_verifies():
         res = subprocess.run([cli] + args + ["--iterations", "3", "--verify"], capture_output=True, text=True, timeout=300)
         assert res.returncode == 0, res.stdout + res.stderr
         assert "Disposition: Passed" in res.stdout
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mnk", [(256, 512, 512), (130, 208, 320), (1024, 768, 2048)])
+def test_fp4_output_epilogue_equals_quantizing_the_bf16_output(Q, mnk, mode):
+    """The NVFP4-output epilogue (for chained GEMMs; the reference's CUTLASS example has the same
+    E2M1 + scale-factor output, cutlass_gemm/nvfp4_gemm.cu:106-108) gives, bit for bit, the quantizer's
+    result on the bf16 output with the same per-tensor maximum -- exact, a generous bound, or one that
+    is too small (saturation)."""
+    from nvfp4_sm120_b200 import _lib, quant
+    m, n, k = mnk
+    qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 31).cuda())
+    qb = Q.quant_nvfp4(O.synthetic_tensor(n, k, 32).cuda())
+    try:
+        _lib.lib().nvfp4_gemm_set_mode(mode)
+        y = Q.nvfp4_mm(qa, qb.t(), out_dtype=torch.bfloat16)
+        exact = quant.tensor_amax(y)
+        for factor in (1.0, 1.5, 0.25):
+            amax = exact * factor
+            got = Q.nvfp4_mm_fp4out(qa, qb.t(), amax)
+            want = Q.quant_nvfp4(y, amax=amax)
+            assert torch.equal(got.qdata, want.qdata), (mnk, mode, factor)
+            assert torch.equal(got.scale.view(torch.uint8), want.scale.view(torch.uint8)), (mnk, mode, factor)
+            assert torch.equal(got.per_tensor_scale, want.per_tensor_scale)
+    finally:
+        _lib.lib().nvfp4_gemm_set_mode(0)
+    assert Q.gemm_status() == 0
+    # and the quantized output feeds the next GEMM directly
+    w2 = Q.quant_nvfp4(O.synthetic_tensor(64, n, 33).cuda())
+    z = Q.nvfp4_mm(got, w2.t(), out_dtype=torch.float32)
+    assert torch.isfinite(z).all()
