@@ -87,6 +87,24 @@ int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
                         uint8_t* qdata, uint8_t* scales, float* pts_out, void* stream);
 
 /*
+ * nvfp4_quantize_bf16 for a tensor that is one SHARD of a larger one (tensor parallelism): the
+ * stochastic-rounding counter of an output block (out_row, k/16) is
+ *     out_row * counter_pitch + counter_base + k/16
+ * instead of the block's index in the shard, so that a shard draws the random bits the whole tensor
+ * would draw for the same elements and the sharded result is bit-identical to the corresponding part
+ * of the unsharded one (given the group-reduced amax).  Examples: a [T, N/p] column shard (rank r)
+ * quantized along N: pitch = N/16, base = r * (N/p)/16; the same shard quantized transposed (output
+ * rows = its N/p columns, blocks along T): pitch = T/16, base = r * (N/p) * (T/16).
+ * nvfp4_quantize_bf16 is this call with pitch = K/16 and base = 0.  No counterpart in the reference
+ * (it is single-GPU).
+ */
+int nvfp4_quantize_shard_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld,
+                              int transpose, int mode, int rht, const float* signs16,
+                              const float* amax, uint64_t philox_seed, uint64_t philox_offset,
+                              uint64_t counter_pitch, uint64_t counter_base,
+                              uint8_t* qdata, uint8_t* scales, float* pts_out, void* stream);
+
+/*
  * The same quantization as nvfp4_amax_bf16 + nvfp4_quantize_bf16(transpose == 0) in ONE launch:
  * a persistent cooperative kernel finds the per-tensor maximum, crosses a grid-wide barrier and
  * quantizes, keeping as much of the tensor as fits in shared memory between the two phases so

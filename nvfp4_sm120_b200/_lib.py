@@ -20,6 +20,10 @@ _SIGS = {
     "nvfp4_quantize_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
                                        _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_uint64, _c.c_uint64,
                                        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    "nvfp4_quantize_shard_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
+                                             _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_uint64, _c.c_uint64,
+                                             _c.c_uint64, _c.c_uint64, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                             _c.c_void_p]),
     "nvfp4_quantize_fused_workspace_bytes": (_c.c_size_t, []),
     "nvfp4_quantize_fused_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
                                              _c.c_void_p, _c.c_uint64, _c.c_uint64, _c.c_void_p, _c.c_void_p,

@@ -154,7 +154,10 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* __restr
                                                          uint64_t seed, uint64_t offset,
                                                          uint8_t* __restrict__ qdata,
                                                          uint8_t* __restrict__ scales,
-                                                         float* __restrict__ pts_out) {
+                                                         float* __restrict__ pts_out,
+                                                         uint64_t ctr_pitch, uint64_t ctr_base) {
+  // Philox counter of block (row, kb) = row * ctr_pitch + ctr_base + kb: the block's index in the
+  // whole tensor when x is a column shard of it (pitch = blocks per row of the whole tensor)
   const GlobalScale g = global_scale(amax);
   if (blockIdx.x == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
   float sg[16];
@@ -180,7 +183,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* __restr
       hadamard16_inplace(v);
     }
     uint32_t lo, hi, sf;
-    encode_block<SR>(v, g, (uint64_t)i, seed, offset, lo, hi, sf);
+    encode_block<SR>(v, g, (uint64_t)r * ctr_pitch + ctr_base + (uint64_t)kb, seed, offset, lo, hi, sf);
     *reinterpret_cast<uint2*>(qdata + i * 8) = make_uint2(lo, hi);
     scales[sf_offset(r, kb, col_tiles)] = (uint8_t)sf;
   }
@@ -241,7 +244,9 @@ __global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restr
                                                          uint64_t seed, uint64_t offset,
                                                          uint8_t* __restrict__ qdata,
                                                          uint8_t* __restrict__ scales,
-                                                         float* __restrict__ pts_out) {
+                                                         float* __restrict__ pts_out,
+                                                         uint64_t ctr_pitch, uint64_t ctr_base) {
+  // Philox counter of output block (column c, row block kb) = c * ctr_pitch + ctr_base + kb
   const GlobalScale g = global_scale(amax);
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
   float sg[16];
@@ -263,8 +268,8 @@ __global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restr
       load_col_pair_block<RHT>(x, ld, r0, c, sg, v0, v1);
       const uint64_t kb = (uint64_t)(r0 >> 4);
       uint32_t sf0, sf1;
-      encode_block<SR>(v0, g, (uint64_t)c * blk_per_orow + kb, seed, offset, q[0][2 * j], q[0][2 * j + 1], sf0);
-      encode_block<SR>(v1, g, (uint64_t)(c + 1) * blk_per_orow + kb, seed, offset, q[1][2 * j], q[1][2 * j + 1], sf1);
+      encode_block<SR>(v0, g, (uint64_t)c * ctr_pitch + ctr_base + kb, seed, offset, q[0][2 * j], q[0][2 * j + 1], sf0);
+      encode_block<SR>(v1, g, (uint64_t)(c + 1) * ctr_pitch + ctr_base + kb, seed, offset, q[1][2 * j], q[1][2 * j + 1], sf1);
       sfw[0] |= sf0 << (8 * j);
       sfw[1] |= sf1 << (8 * j);
       nvalid = j + 1;
@@ -407,13 +412,14 @@ extern "C" int nvfp4_amax_bf16(const void* x, int64_t rows, int64_t cols, int64_
 namespace nvfp4 { namespace fused {
 int quantize_rows_known_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
                              const float* signs16, const float* amax, uint64_t seed, uint64_t offset,
+                             uint64_t counter_pitch, uint64_t counter_base,
                              uint8_t* qdata, uint8_t* scales, float* pts_out, cudaStream_t stream);
 }}
 
-extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
-                                   int mode, int rht, const float* signs16, const float* amax,
-                                   uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
-                                   float* pts_out, void* stream_) {
+extern "C" int nvfp4_quantize_shard_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
+                                         int mode, int rht, const float* signs16, const float* amax,
+                                         uint64_t seed, uint64_t offset, uint64_t counter_pitch, uint64_t counter_base,
+                                         uint8_t* qdata, uint8_t* scales, float* pts_out, void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (x == nullptr || amax == nullptr || qdata == nullptr || scales == nullptr || (rht && signs16 == nullptr))
     return NVFP4_E_NULL;
@@ -430,7 +436,7 @@ extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, in
     // row-wise output with the maximum given: one streaming pass of the single-launch kernel's
     // quantize phase (it declines only tensors of 2^31 blocks or more, which the plain kernel takes)
     const int rc = nvfp4::fused::quantize_rows_known_amax(x, rows, cols, ld, mode, rht, signs16, amax, seed, offset,
-                                                          qdata, scales, pts_out, stream);
+                                                          counter_pitch, counter_base, qdata, scales, pts_out, stream);
     if (rc != NVFP4_E_LIMIT) return rc;
   }
   // padding of the tiled scale buffer must read as zero (the reference pads with zeros)
@@ -444,7 +450,7 @@ extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, in
     const int bpr = (int)(cols >> 4);
     const int grid = grid_for(rows * bpr, 256, 1 << 30);
 #define NVFP4_LAUNCH_ROWS(SR_, RHT_) \
-    quant_rows_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, bpr, ld, signs16, amax, seed, offset, qdata, scales, pts_out)
+    quant_rows_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, bpr, ld, signs16, amax, seed, offset, qdata, scales, pts_out, counter_pitch, counter_base)
     if (sr && rht) NVFP4_LAUNCH_ROWS(true, true);
     else if (sr) NVFP4_LAUNCH_ROWS(true, false);
     else if (rht) NVFP4_LAUNCH_ROWS(false, true);
@@ -454,7 +460,7 @@ extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, in
     dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
     if (grid.y > 65535u) return NVFP4_E_SHAPE;
 #define NVFP4_LAUNCH_COLS(SR_, RHT_) \
-    quant_cols_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax, seed, offset, qdata, scales, pts_out)
+    quant_cols_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax, seed, offset, qdata, scales, pts_out, counter_pitch, counter_base)
     if (sr && rht) NVFP4_LAUNCH_COLS(true, true);
     else if (sr) NVFP4_LAUNCH_COLS(true, false);
     else if (rht) NVFP4_LAUNCH_COLS(false, true);
@@ -491,4 +497,14 @@ extern "C" int nvfp4_quantize_weight_bf16(const void* w, int64_t rows, int64_t c
     quant_weight_dual_kernel<false><<<grid, 256, 0, stream>>>(wp, rows, cols, ld, amax, qdata_rows, scales_rows, qdata_cols,
                                                               scales_cols, pts_out);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+
+extern "C" int nvfp4_quantize_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int transpose,
+                                   int mode, int rht, const float* signs16, const float* amax,
+                                   uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
+                                   float* pts_out, void* stream_) {
+  // the tensor is whole: a block's counter is its index in x (or in x^T): out_row * (K / 16) + k / 16
+  const uint64_t pitch = (uint64_t)((transpose ? rows : cols) / 16);
+  return nvfp4_quantize_shard_bf16(x, rows, cols, ld, transpose, mode, rht, signs16, amax, seed, offset, pitch, 0,
+                                   qdata, scales, pts_out, stream_);
 }

@@ -386,22 +386,28 @@ int device_info(DeviceInfo& out) {
 namespace nvfp4 { namespace tiled {
 int launch(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht, const float* signs16,
            uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales, float* pts_out, void* workspace,
-           const float* amax_in, unsigned long long wait_limit_ns, uint32_t extra_arrivals, cudaStream_t stream);
+           const float* amax_in, unsigned long long wait_limit_ns, uint32_t extra_arrivals, uint64_t counter_pitch,
+           uint64_t counter_base, cudaStream_t stream);
 }}
 
 static int launch_fused(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
                         const float* signs16, uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales,
-                        float* pts_out, void* workspace, const float* amax_in, cudaStream_t stream) {
+                        float* pts_out, void* workspace, const float* amax_in, cudaStream_t stream,
+                        uint64_t counter_pitch = 0, uint64_t counter_base = 0) {
+  // counter_pitch / counter_base: Philox counter of block (row, kb) = row * pitch + base + kb (a column
+  // shard of a larger tensor numbers its blocks as the whole tensor does); 0 / 0 = the block's own index
+  if (counter_pitch == 0) counter_pitch = (uint64_t)(cols / 16);
+  const bool whole = counter_pitch == (uint64_t)(cols / 16) && counter_base == 0;
   // Kernel choice.  With the maximum given, the tile-form kernel (quantize_tiled.cu) is the faster one
   // (15.9 / 20.5 / 23.7 us against 19.8 / 22.2 / 24.6 us at 8192 x 4096 in the three modes); for the
   // two-phase launch the range-form kernel below is (26.6 / 30.1 / 35.5 us against 26.4 / 31.6 / 37.3).
   // NVFP4_QUANT_TILED = 0 / 1 forces one of them for both cases (measurements, tests).
   static const int force_tiled = []() { const char* e = getenv("NVFP4_QUANT_TILED"); return e == nullptr ? -1 : atoi(e); }();
-  const bool use_tiled = force_tiled < 0 ? amax_in != nullptr : force_tiled != 0;
+  const bool use_tiled = (force_tiled < 0 ? amax_in != nullptr : force_tiled != 0) || !whole;
   if (use_tiled)
     return nvfp4::tiled::launch(x, rows, cols, ld, mode, rht, signs16, seed, offset, qdata, scales, pts_out, workspace,
                                 amax_in, g_wait_ns.load(std::memory_order_relaxed),
-                                g_extra_arrivals.load(std::memory_order_relaxed), stream);
+                                g_extra_arrivals.load(std::memory_order_relaxed), counter_pitch, counter_base, stream);
   DeviceInfo info;
   const int irc = device_info(info);
   if (irc != NVFP4_OK) return irc;
@@ -485,11 +491,14 @@ namespace nvfp4 { namespace fused {
 // kernel).
 int quantize_rows_known_amax(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht,
                              const float* signs16, const float* amax, uint64_t seed, uint64_t offset,
+                             uint64_t counter_pitch, uint64_t counter_base,
                              uint8_t* qdata, uint8_t* scales, float* pts_out, cudaStream_t stream) {
   const int rc = check_fused_args(x, rows, cols, ld, mode, rht, signs16, qdata, scales);
   if (rc != NVFP4_OK) return rc;
+  // the tile kernel keeps the counter in 32 bits: larger global indices go to the plain kernel
+  if ((uint64_t)rows * counter_pitch + counter_base >= (1ull << 32)) return NVFP4_E_LIMIT;
   return launch_fused(x, rows, cols, ld, mode, rht, signs16, seed, offset, qdata, scales, pts_out, nullptr, amax,
-                      stream);
+                      stream, counter_pitch, counter_base);
 }
 }}
 

@@ -50,6 +50,7 @@ enum : int { kErrBarrier = 1, kErrCopy = 2 };
 struct Params {
   uint32_t rows, bpr;            // rows of x, 16-element blocks per row
   uint32_t ntc, ntiles;          // column tiles per row of tiles, tiles in all
+  uint32_t ctr_pitch, ctr_base;  // Philox counter of block (row, kb) = row * ctr_pitch + ctr_base + kb
   uint64_t q_pitch;              // bytes per row of qdata (cols / 2)
   const float* signs16;
   PhiloxKeys keys;
@@ -94,7 +95,7 @@ struct Cursor {
   bool inside;
 };
 struct CursorConst {
-  uint32_t ntc, rows, bpr, row_t, kb;
+  uint32_t ntc, rows, bpr, row_t, kb, ctr_pitch, ctr_base;
   uint64_t q_wrap;       // from the last tile of a row of tiles to the first of the next: 128 rows down, back to column 0
   uint32_t i_wrap;
 };
@@ -104,7 +105,7 @@ __device__ __forceinline__ void cursor_set(Cursor& c, const CursorConst& k, uint
   c.ct = tile - c.rt * k.ntc;
   c.q = qdata + (uint64_t)c.rt * (128u * q_pitch) + c.ct * 32u + q_lane;
   c.s = scales + (uint64_t)tile * 512u + sc_lane;
-  c.i = (c.rt * 128u + k.row_t) * k.bpr + c.ct * 4u + k.kb;
+  c.i = (c.rt * 128u + k.row_t) * k.ctr_pitch + k.ctr_base + c.ct * 4u + k.kb;
   c.inside = c.rt * 128u + k.row_t < k.rows && c.ct * 4u + k.kb < k.bpr;
 }
 __device__ __forceinline__ void cursor_step(Cursor& c, const CursorConst& k) {
@@ -165,7 +166,8 @@ quant_tiled_kernel(const __grid_constant__ CUtensorMap map_x, const Params p) {
   const uint32_t off1 = row_t * 128u + (((2u * kb + 1u) ^ (row_t & 7u)) << 4);   // of row r sits at c ^ (r & 7)
   const uint32_t sc_lane = (2u * wsub + hrow) * 16u + grp * 4u + kb;             // byte inside the 512-byte scale tile
   const uint64_t q_lane = (uint64_t)row_t * p.q_pitch + kb * 8u;
-  const CursorConst cc{p.ntc, p.rows, p.bpr, row_t, kb, 128ull * p.q_pitch - 32ull * p.ntc, 128u * p.bpr - 4u * p.ntc};
+  const CursorConst cc{p.ntc, p.rows, p.bpr, row_t, kb, p.ctr_pitch, p.ctr_base,
+                       128ull * p.q_pitch - 32ull * p.ntc, 128u * p.ctr_pitch - 4u * p.ntc};
   uint32_t sm[8];                 // sign-bit masks of the packed bf16 pairs (bit 15: even, bit 31: odd)
 #pragma unroll
   for (int j = 0; j < 8; ++j)
@@ -460,7 +462,8 @@ int device_info(DeviceInfo& out) {
 // launch.  Arguments have been validated by the caller (quantize_fused.cu).
 int launch(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int rht, const float* signs16,
            uint64_t seed, uint64_t offset, uint8_t* qdata, uint8_t* scales, float* pts_out, void* workspace,
-           const float* amax_in, unsigned long long wait_limit_ns, uint32_t extra_arrivals, cudaStream_t stream) {
+           const float* amax_in, unsigned long long wait_limit_ns, uint32_t extra_arrivals, uint64_t counter_pitch,
+           uint64_t counter_base, cudaStream_t stream) {
   DeviceInfo info;
   const int irc = device_info(info);
   if (irc != NVFP4_OK) return irc;
@@ -486,6 +489,8 @@ int launch(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode, int 
   const uint64_t ntiles = (uint64_t)((rows + kTileRows - 1) / kTileRows) * p.ntc;
   if (ntiles >= (1ull << 31)) return NVFP4_E_LIMIT;
   p.ntiles = (uint32_t)ntiles;
+  p.ctr_pitch = (uint32_t)counter_pitch;
+  p.ctr_base = (uint32_t)counter_base;
   p.q_pitch = (uint64_t)(cols / 2);
   p.signs16 = signs16;
   for (int r = 0; r < 10; ++r) {

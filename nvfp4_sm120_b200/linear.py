@@ -106,7 +106,7 @@ class FP4LinearFn(torch.autograd.Function):
                 x_amax_rht=True):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
-        x_sharded, y_sharded = sharded                 # is the K dim / the N dim split across ranks?
+        x_sharded, y_sharded = sharded[0], sharded[1]  # is the K dim / the N dim split across ranks?
         # x_amax: fp32 [2] from a fused producer = max|x| and max|RHT_tokens(x)| (what the two amax
         # passes over x would find); the token count must then be a multiple of 16
         if x_amax is not None and (x2.shape[0] % BLK != 0 or x2.dtype != torch.bfloat16):
@@ -132,8 +132,16 @@ class FP4LinearFn(torch.autograd.Function):
     def backward(ctx, gy):
         x2, w = ctx.saved_tensors
         H, signs, wq_N, red = ctx.H, ctx.signs, ctx.wq_N, ctx.amax_reduce
-        x_sharded, y_sharded = ctx.sharded
+        x_sharded, y_sharded = ctx.sharded[0], ctx.sharded[1]
         gy2 = gy.reshape(-1, w.shape[0])
+        # a gradient split along N draws the stochastic-rounding bits of its place in the whole tensor:
+        # sharded = (x_sharded, y_sharded, (rank, world)) gives the place (see nvfp4_quantize_shard_bf16)
+        ctr_rows = ctr_cols = None
+        if y_sharded and len(ctx.sharded) > 2 and ctx.sharded[2] is not None:
+            rank, world = ctx.sharded[2]
+            n_local, tokens = w.shape[0], gy2.shape[0]
+            ctr_rows = (n_local * world // BLK, rank * n_local // BLK)
+            ctr_cols = (tokens // BLK, rank * n_local * (tokens // BLK))
         g_amax, g_amax_rht = _take_grad_amax(gy2, signs)      # known to a fused producer of gy, else None
         g_red = red if y_sharded else None
         if g_amax is not None and g_red is not None:
@@ -148,26 +156,29 @@ class FP4LinearFn(torch.autograd.Function):
         dx = dw = None
         if ctx.needs_input_grad[0]:
             # dgrad: dX = dY @ W, contraction over N; dY gets stochastic rounding
-            gq = _quant(gy2, None if g_amax is not None else g_red, stochastic=True, amax=g_amax)
+            gq = _quant(gy2, None if g_amax is not None else g_red, stochastic=True, amax=g_amax, counter=ctr_rows)
             if wq_N is None:
                 wq_N = _quant(w, red, transpose=True)
             dx = nvfp4_mm(gq, wq_N.t(), torch.bfloat16).reshape(ctx.xshape).to(gy.dtype)
         if ctx.needs_input_grad[1]:
             # wgrad: dW = dY^T @ X, contraction over tokens; Hadamard on both, SR on the gradient
             gtq = _quant(gy2, None if g_amax_rht is not None else g_red, stochastic=True, rht=True, H=H, signs=signs,
-                         transpose=True, amax=g_amax_rht)
+                         transpose=True, amax=g_amax_rht, counter=ctr_cols)
             xtq = _quant(x2, xt_red, rht=True, H=H, signs=signs, transpose=True, amax=x_amax_rht)
             dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
         return dx, dw, None, None, None, None, None, None, None, None
 
 
-def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False, amax=None):
-    """amax: the per-tensor maximum if a producer already knows it (this rank's part when sharded)."""
+def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False, amax=None, counter=None):
+    """amax: the per-tensor maximum if a producer already knows it (this rank's part when sharded);
+    counter: (pitch, base) of the stochastic-rounding counter of a shard."""
     if amax_reduce is None:
-        return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose, amax=amax)
+        if counter is not None and amax is None:
+            amax = tensor_amax(t, rht, signs, transpose)
+        return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose, amax=amax, counter=counter)
     amax = tensor_amax(t, rht, signs, transpose) if amax is None else amax.clone()
     amax_reduce(amax)
-    return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose, amax=amax)
+    return quant_nvfp4(t, stochastic, rht, H, signs, transpose=transpose, amax=amax, counter=counter)
 
 
 class WeightQuantCache:

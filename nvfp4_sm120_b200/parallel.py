@@ -125,7 +125,10 @@ class ColumnParallelFP4Linear(_ParallelLinearBase):
         layers from one copy so that their input gradients are summed locally and all-reduced once)."""
         if not copied:
             x = _CopyToGroup.apply(x, self.group)
-        return self._call(x, (False, True))
+        place = None
+        if dist.is_available() and dist.is_initialized():
+            place = (dist.get_rank(self.group), dist.get_world_size(self.group))
+        return self._call(x, (False, True, place))
 
 
 class RowParallelFP4Linear(_ParallelLinearBase):

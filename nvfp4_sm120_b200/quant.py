@@ -102,7 +102,7 @@ def tensor_amax(t, rht=False, signs=None, transpose=False, out=None):
 
 
 def quant_nvfp4(t, stochastic=False, rht=False, H=None, signs=None, seed=None, *,
-                transpose=False, amax=None, philox_offset=0, fused=True):
+                transpose=False, amax=None, philox_offset=0, fused=True, counter=None):
     """t: [M, K] -> NVFP4Tensor blocked along K (K % 16 == 0), as nvfp4_gemm.py:30-48.
 
     transpose=True quantizes t.t() (blocks along the rows of t) without materialising the
@@ -111,7 +111,11 @@ def quant_nvfp4(t, stochastic=False, rht=False, H=None, signs=None, seed=None, *
     maximum here (a tensor sharded across GPUs passes the all-reduced maximum).
     seed=None takes the module counter and advances it on stochastic calls.
     fused=False forces the two-launch path (amax kernel, then quantize kernel) where the
-    single-launch cooperative kernel would be used; both give the same bytes."""
+    single-launch cooperative kernel would be used; both give the same bytes.
+    counter: (pitch, base) of the stochastic-rounding counter when t is a shard of a larger tensor
+    (see nvfp4_quantize_shard_bf16 in the C header); needs amax (the group-reduced one)."""
+    if counter is not None and amax is None:
+        raise ValueError("a sharded tensor is quantized with the group-reduced amax: pass amax=")
     if seed is None:
         seed = _SEED[0]
         if stochastic:
@@ -141,13 +145,14 @@ def quant_nvfp4(t, stochastic=False, rht=False, H=None, signs=None, seed=None, *
         return NVFP4Tensor(qdata, scale.view(torch.float8_e4m3fn), BLK, t.dtype, pts, True)
     if amax is None:
         amax = tensor_amax(x, rht, sg, transpose)
+    pitch, base = (k // BLK, 0) if counter is None else (int(counter[0]), int(counter[1]))
     with torch.cuda.device(dev):
-        code = _lib.lib().nvfp4_quantize_bf16(
+        code = _lib.lib().nvfp4_quantize_shard_bf16(
             x.data_ptr(), rows, cols, x.stride(0), int(transpose),
             _lib.ROUND_STOCHASTIC if stochastic else _lib.ROUND_NEAREST, int(rht),
             sg.data_ptr() if rht else None, amax.data_ptr(), int(seed) & (2 ** 64 - 1), int(philox_offset),
-            qdata.data_ptr(), scale.data_ptr(), pts.data_ptr(), _stream(dev))
-    _lib.check(code, "nvfp4_quantize_bf16")
+            pitch, base, qdata.data_ptr(), scale.data_ptr(), pts.data_ptr(), _stream(dev))
+    _lib.check(code, "nvfp4_quantize_shard_bf16")
     return NVFP4Tensor(qdata, scale.view(torch.float8_e4m3fn), BLK, t.dtype, pts, True)
 
 

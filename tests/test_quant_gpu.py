@@ -227,3 +227,32 @@ def test_single_launch_strided_input(Q):
     a = Q.quant_nvfp4(view, fused=True)
     b = Q.quant_nvfp4(view.contiguous(), fused=False)
     assert torch.equal(a.qdata, b.qdata) and torch.equal(a.scale.view(torch.uint8), b.scale.view(torch.uint8))
+
+
+@pytest.mark.parametrize("rht", [False, True])
+def test_shard_counters_reproduce_the_whole_tensor(Q, rht):
+    """A column shard quantized with the whole tensor's amax and the shard's counter pitch / base
+    (nvfp4_quantize_shard_bf16) gives the bytes of the corresponding part of the unsharded
+    quantization, stochastic rounding included -- row-wise and transposed."""
+    x = O.synthetic_tensor(256, 512, 61).cuda()
+    s = O.signs_from_seed(1).cuda()
+    c0, c1 = 128, 384
+    shard = x[:, c0:c1]
+    # row-wise (blocks along the columns): the Hadamard runs inside a block, so shards commute with it
+    full = Q.quant_nvfp4(x, stochastic=True, rht=rht, signs=s, seed=5)
+    amax = Q.tensor_amax(x, rht=rht, signs=s)
+    part = Q.quant_nvfp4(shard, stochastic=True, rht=rht, signs=s, seed=5, amax=amax,
+                         counter=(512 // 16, c0 // 16))
+    assert torch.equal(part.qdata, full.qdata[:, c0 // 2:c1 // 2])
+    full_sc = O.unswizzle_scales(full.scale.view(torch.uint8).cpu(), 256, 512)
+    part_sc = O.unswizzle_scales(part.scale.view(torch.uint8).cpu(), 256, c1 - c0)
+    assert torch.equal(part_sc, full_sc[:, c0 // 16:c1 // 16])
+    # transposed (output rows = columns of x, blocks along the rows of x)
+    full_t = Q.quant_nvfp4(x, stochastic=True, rht=rht, signs=s, seed=6, transpose=True)
+    amax_t = Q.tensor_amax(x, rht=rht, signs=s, transpose=True)
+    part_t = Q.quant_nvfp4(shard, stochastic=True, rht=rht, signs=s, seed=6, transpose=True, amax=amax_t,
+                           counter=(256 // 16, c0 * (256 // 16)))
+    assert torch.equal(part_t.qdata, full_t.qdata[c0:c1])
+    full_tsc = O.unswizzle_scales(full_t.scale.view(torch.uint8).cpu(), 512, 256)
+    part_tsc = O.unswizzle_scales(part_t.scale.view(torch.uint8).cpu(), c1 - c0, 256)
+    assert torch.equal(part_tsc, full_tsc[c0:c1])

@@ -62,9 +62,12 @@ def main():
         print(f"rank {rank} amortize={amort}: y {e_y:.4f} dx {e_dx:.4f} dW_gate {e_gw:.4f} dW_down {e_dw:.4f} "
               f"(1-GPU quantization error vs exact {e_q:.4f})", flush=True)
         assert e_y < 0.02, e_y                       # bf16 reduction order only
-        # gradients carry independent stochastic-rounding draws on the sharded tensors: same level as
-        # the quantization error itself
-        assert e_dx < 0.3 and e_gw < 0.3 and e_dw < 0.3
+        # A shard draws the stochastic-rounding bits of its place in the whole tensor and uses the
+        # group-reduced maxima, so its quantized operands are those of the 1-GPU run: the weight
+        # gradients (no reduction across ranks) agree to the GEMM tolerance, the input gradient to the
+        # bf16 order of summation of the all-reduce
+        assert e_dx < 0.02, e_dx
+        assert e_gw < 2e-3 and e_dw < 2e-3, (e_gw, e_dw)
         assert Q.gemm_status() == 0
     Q.set_amortize(False)
 
