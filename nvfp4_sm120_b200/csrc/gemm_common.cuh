@@ -201,8 +201,9 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, int64_t row, in
         p.d_sf[sf_offset(row, (col >> 4) + b, col_tiles)] = (uint8_t)sf;
       }
     }
-    if (full) *reinterpret_cast<uint4*>(q) = make_uint4(w[0], w[1], w[2], w[3]);
-    else *reinterpret_cast<uint2*>(q) = make_uint2(w[0], w[1]);
+    // a row of N / 2 bytes starts on an 8-byte boundary (N % 16 == 0), not always on a 16-byte one
+    *reinterpret_cast<uint2*>(q) = make_uint2(w[0], w[1]);
+    if (full) *reinterpret_cast<uint2*>(q + 8) = make_uint2(w[2], w[3]);
     return;
   }
   if (p.splits > 1) {                                   // split-K partial sum (fp32 output only)
