@@ -432,11 +432,15 @@ def run_gpu_arm(args, rank, world, local_rank):
         except Exception as exc:
             tp = {"error": f"{type(exc).__name__}: {exc}"[:300]}
         try:
+            tp_fused = extras_tensor_parallel(Q, dev, rank, world, dist, fuse_gate_up=True)
+        except Exception as exc:
+            tp_fused = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        try:
             dp = extras_data_parallel(Q, dev, rank, world, dist, backends=("fp4",))
         except Exception as exc:
             dp = {"error": f"{type(exc).__name__}: {exc}"[:300]}
         if rank == 0:
-            line["extras"] = {"ffn_tensor_parallel": tp, "dp_gpt124m": dp}
+            line["extras"] = {"ffn_tensor_parallel": tp, "ffn_tensor_parallel_fused_gate_up": tp_fused, "dp_gpt124m": dp}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -484,7 +488,7 @@ def extras_data_parallel(Q, dev, rank, world, dist, backends=("fp4", "bf16")):
     return res
 
 
-def extras_tensor_parallel(Q, dev, rank, world, dist):
+def extras_tensor_parallel(Q, dev, rank, world, dist, fuse_gate_up=False):
     """benchmark config 4 over `world` GPUs: SwiGLU d 4096 / h 14336 split column- (gate, up) and row-wise
     (down), 8 microbatches x 4096 tokens, forward + backward, amortized weight quantization; NCCL
     all-reduce of the amax words and of the row-parallel output / column-parallel input gradient.
@@ -496,7 +500,8 @@ def extras_tensor_parallel(Q, dev, rank, world, dist):
     bd, bh = 1.0 / d_model ** 0.5, 1.0 / hidden ** 0.5
     hs = hidden // world
     mk = lambda r, c, b: (torch.rand(r, c, device=dev, generator=g) * 2 - 1) * b
-    ffn = P.TensorParallelSwiGLU(mk(hs, d_model, bd), mk(hs, d_model, bd), mk(d_model, hs, bh), device=dev)
+    ffn = P.TensorParallelSwiGLU(mk(hs, d_model, bd), mk(hs, d_model, bd), mk(d_model, hs, bh), device=dev,
+                                 fuse_gate_up=fuse_gate_up)
     gx = torch.Generator(device=dev).manual_seed(40)              # activations are replicated
     xs = [torch.randn(tokens, d_model, device=dev, dtype=torch.bfloat16, generator=gx).requires_grad_(True)
           for _ in range(micro)]
@@ -551,7 +556,8 @@ def extras_tensor_parallel(Q, dev, rank, world, dist):
     return {"ms_per_step": ms, "tflops_all_gpus": micro * ffn_flops(tokens, d_model, hidden) / ms / 1e9,
             "eager_ms_per_step": eager_ms, "graph_ms_per_step": None if float(t[2]) < 0 else float(t[2]),
             "graph": graph_note, "scaling": "strong", "tp": world, "gemm_status": Q.gemm_status(),
-            "config": "SwiGLU d4096 h14336, 8 microbatches x 4096 tokens, fwd+bwd, TP over NCCL"}
+            "config": "SwiGLU d4096 h14336, 8 microbatches x 4096 tokens, fwd+bwd, TP over NCCL" +
+                      (", gate|up as one column-parallel projection, dX all-reduce beside the wgrad GEMM" if fuse_gate_up else "")}
 
 
 def library_fp4_mm(qa, qb):
@@ -657,8 +663,11 @@ def extras(Q, dev, bf16_peak, peak_kind):
     gy = torch.randn(tokens, d_model, device=dev, dtype=torch.bfloat16, generator=g)
     ffn = {}
     Q.set_amortize(True)
-    for name in ("fp4", "bf16"):
-        m = SwiGLUFFN(d_model, hidden, use_fp4=(name == "fp4"), device=dev, seed=4)
+    for name in ("fp4", "fp4_fused_gate_up", "bf16"):
+        # "fp4": three FP4Linear as the benchmark config words it; "fp4_fused_gate_up": the same block
+        # with gate and up kept as one [2h, d] projection (one quantization of x per layout, one dgrad GEMM)
+        m = SwiGLUFFN(d_model, hidden, use_fp4=(name != "bf16"), device=dev, seed=4,
+                      fuse_gate_up=(name == "fp4_fused_gate_up"))
         if name == "bf16":
             m = m.to(torch.bfloat16)
 
@@ -682,6 +691,7 @@ def extras(Q, dev, bf16_peak, peak_kind):
         torch.cuda.empty_cache()
     Q.set_amortize(False)
     ffn["speedup_vs_bf16"] = ffn["bf16"]["ms_per_step"] / ffn["fp4"]["ms_per_step"]
+    ffn["speedup_vs_bf16_fused_gate_up"] = ffn["bf16"]["ms_per_step"] / ffn["fp4_fused_gate_up"]["ms_per_step"]
     ffn["config"] = "SwiGLU d4096 h14336, 8 microbatches x 4096 tokens, fprop RNE / dgrad SR / wgrad RHT+SR, 1 GPU"
     out["ffn_fwd_bwd"] = ffn
     out["gemm_status"] = Q.gemm_status()

@@ -241,6 +241,16 @@ int nvfp4_swiglu_bwd_bf16(const void* gate, const void* up, const void* dout, in
                           float* maxima4, int zero_first, void* stream);
 
 /*
+ * nvfp4_swiglu_bwd_bf16 with its own leading dimension for dout: gate and up may then be the two
+ * halves of one [rows, 2 cols] tensor (a fused gate|up projection, ld_in = 2 cols) while dout is a
+ * plain [rows, cols] tensor, and dgate / dup the two halves of one [rows, 2 cols] gradient
+ * (ld_out = 2 cols) that the fused projection's backward consumes as it is.
+ */
+int nvfp4_swiglu_bwd_strided_bf16(const void* gate, const void* up, const void* dout, int64_t rows, int64_t cols,
+                                  int64_t ld_in, int64_t ld_dout, void* dgate, void* dup, int64_t ld_out,
+                                  const float* signs16, float* maxima4, int zero_first, void* stream);
+
+/*
  * The same producer fusion for the squared-ReLU MLP of the reference's models
  * (nvfp4_train.py:120-123): out = relu(x)^2, and backward dx = 2 relu(x) * dout, each with
  * maxima2 = {max|result|, max|RHT_rows(result)|} as above.  Only for 16-byte rows (cols, ld_in,

@@ -40,6 +40,9 @@ _SIGS = {
     "nvfp4_swiglu_bwd_bf16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64,
                                          _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int,
                                          _c.c_void_p]),
+    "nvfp4_swiglu_bwd_strided_bf16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64,
+                                                 _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int64,
+                                                 _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nvfp4_relu2_fwd_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_int64,
                                         _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nvfp4_relu2_bwd_bf16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p,

@@ -134,7 +134,8 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const uint16_t* __restr
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint16_t* __restrict__ gate,
                                                          const uint16_t* __restrict__ up,
                                                          const uint16_t* __restrict__ dh, int64_t rows,
-                                                         int64_t cols, int64_t ld_in, uint16_t* __restrict__ dgate,
+                                                         int64_t cols, int64_t ld_in, int64_t ld_dh,
+                                                         uint16_t* __restrict__ dgate,
                                                          uint16_t* __restrict__ dup, int64_t ld_out,
                                                          const float* __restrict__ signs16,
                                                          float* __restrict__ maxima) {
@@ -151,7 +152,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint16_t* __restr
       const int nrow = (int)min((int64_t)16, rows - r0);
       const uint32_t* pg = reinterpret_cast<const uint32_t*>(gate + r0 * ld_in + c);
       const uint32_t* pu = reinterpret_cast<const uint32_t*>(up + r0 * ld_in + c);
-      const uint32_t* pd = reinterpret_cast<const uint32_t*>(dh + r0 * ld_in + c);
+      const uint32_t* pd = reinterpret_cast<const uint32_t*>(dh + r0 * ld_dh + c);
       uint32_t wg[16], wu[16], wd[16];
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
@@ -159,7 +160,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const uint16_t* __restr
         const size_t off = (size_t)i * (size_t)(ld_in >> 1);
         wg[i] = in ? __ldg(pg + off) : 0u;
         wu[i] = in ? __ldg(pu + off) : 0u;
-        wd[i] = in ? __ldg(pd + off) : 0u;
+        wd[i] = in ? __ldg(pd + (size_t)i * (size_t)(ld_dh >> 1)) : 0u;
       }
 #pragma unroll
       for (int i = 0; i < 16; ++i) {                       // wg <- dgate, wu <- dup, in place
@@ -271,7 +272,7 @@ __global__ void __launch_bounds__(256) swiglu_fwd_wide_kernel(const uint16_t* __
 __global__ void __launch_bounds__(256) swiglu_bwd_wide_kernel(const uint16_t* __restrict__ gate,
                                                               const uint16_t* __restrict__ up,
                                                               const uint16_t* __restrict__ dh, int64_t rows,
-                                                              int64_t cols, int64_t ld_in,
+                                                              int64_t cols, int64_t ld_in, int64_t ld_dh,
                                                               uint16_t* __restrict__ dgate, uint16_t* __restrict__ dup,
                                                               int64_t ld_out, const float* __restrict__ signs16,
                                                               float* __restrict__ maxima) {
@@ -295,7 +296,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_wide_kernel(const uint16_t* __
       const bool in = col_in && r < rows;
       const uint4 z = make_uint4(0, 0, 0, 0);
       const uint4 g4 = in ? ldg16(gate + r * ld_in + c0 + cc) : z, u4 = in ? ldg16(up + r * ld_in + c0 + cc) : z;
-      const uint4 d4 = in ? ldg16(dh + r * ld_in + c0 + cc) : z;
+      const uint4 d4 = in ? ldg16(dh + r * ld_dh + c0 + cc) : z;
       const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w}, dw[4] = {d4.x, d4.y, d4.z, d4.w};
       uint32_t og[4], ou[4];
 #pragma unroll
@@ -437,26 +438,36 @@ extern "C" int nvfp4_swiglu_fwd_bf16(const void* gate, const void* up, int64_t r
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 
-extern "C" int nvfp4_swiglu_bwd_bf16(const void* gate, const void* up, const void* dh, int64_t rows, int64_t cols,
-                                     int64_t ld_in, void* dgate, void* dup, int64_t ld_out, const float* signs16,
-                                     float* maxima4, int zero_first, void* stream_) {
+extern "C" int nvfp4_swiglu_bwd_strided_bf16(const void* gate, const void* up, const void* dh, int64_t rows,
+                                             int64_t cols, int64_t ld_in, int64_t ld_dout, void* dgate, void* dup,
+                                             int64_t ld_out, const float* signs16, float* maxima4, int zero_first,
+                                             void* stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int rc = check(gate, up, dh, dgate, dup, rows, cols, ld_in, ld_out, signs16, maxima4);
   if (rc != NVFP4_OK) return rc;
+  if (ld_dout < cols) return NVFP4_E_SHAPE;
+  if ((ld_dout & 1) != 0) return NVFP4_E_ALIGN;
   if (zero_first && cudaMemsetAsync(maxima4, 0, 4 * sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
   const dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
-  if (wide_ok(gate, up, dh, dgate, dup, cols, ld_in, ld_out))
+  if (wide_ok(gate, up, dh, dgate, dup, cols, ld_in, ld_out) && (ld_dout & 7) == 0)
     swiglu_bwd_wide_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate),
                                                       static_cast<const uint16_t*>(up),
-                                                      static_cast<const uint16_t*>(dh), rows, cols, ld_in,
+                                                      static_cast<const uint16_t*>(dh), rows, cols, ld_in, ld_dout,
                                                       static_cast<uint16_t*>(dgate), static_cast<uint16_t*>(dup),
                                                       ld_out, signs16, maxima4);
   else
     swiglu_bwd_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(gate), static_cast<const uint16_t*>(up),
-                                                 static_cast<const uint16_t*>(dh), rows, cols, ld_in,
+                                                 static_cast<const uint16_t*>(dh), rows, cols, ld_in, ld_dout,
                                                  static_cast<uint16_t*>(dgate), static_cast<uint16_t*>(dup), ld_out,
                                                  signs16, maxima4);
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+
+extern "C" int nvfp4_swiglu_bwd_bf16(const void* gate, const void* up, const void* dh, int64_t rows, int64_t cols,
+                                     int64_t ld_in, void* dgate, void* dup, int64_t ld_out, const float* signs16,
+                                     float* maxima4, int zero_first, void* stream_) {
+  return nvfp4_swiglu_bwd_strided_bf16(gate, up, dh, rows, cols, ld_in, ld_in, dgate, dup, ld_out, signs16, maxima4,
+                                       zero_first, stream_);
 }
 
 // Squared ReLU and its backward with the maxima of the result (see relu2_wide_kernel).  Rows of 16

@@ -9,7 +9,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .linear import FP4Linear, make_linear
-from .swiglu import swiglu
+from .swiglu import swiglu, swiglu_packed
 
 
 class SwiGLUFFN(nn.Module):
@@ -17,15 +17,30 @@ class SwiGLUFFN(nn.Module):
     and bf16 activations the SwiGLU product and its backward run as fused kernels that also hand
     the following quantizations their per-tensor maxima (fused=False keeps the torch ops)."""
 
-    def __init__(self, d_model, hidden, use_fp4=True, device="cuda", seed=None, fused=True):
+    def __init__(self, d_model, hidden, use_fp4=True, device="cuda", seed=None, fused=True, fuse_gate_up=False):
+        """fuse_gate_up: keep the gate and up weights as ONE [2 hidden, d_model] projection (rows 0..hidden-1
+        gate, the rest up; same initial values as the two separate linears).  x is then quantized once
+        per layout instead of twice, the two input-gradient GEMMs and their sum become one GEMM over
+        K = 2 hidden, and the SwiGLU kernels read / write the packed [tokens, 2 hidden] tensors in place.
+        The per-tensor scale of the fused weight and of its output gradient spans both halves."""
         super().__init__()
         self.fused = bool(fused and use_fp4)
-        self.gate = make_linear(d_model, hidden, use_fp4, device)
-        self.up = make_linear(d_model, hidden, use_fp4, device)
-        self.down = make_linear(hidden, d_model, use_fp4, device)
+        self.fuse_gate_up = bool(fuse_gate_up and self.fused)
+        self.hidden = hidden
         g = None
         if seed is not None:
             g = torch.Generator(device=device).manual_seed(seed)
+        if self.fuse_gate_up:
+            self.gate_up = make_linear(d_model, 2 * hidden, use_fp4, device)
+            self.down = make_linear(hidden, d_model, use_fp4, device)
+            with torch.no_grad():
+                bound = 1.0 / math.sqrt(d_model)
+                self.gate_up.weight.uniform_(-bound, bound, generator=g)       # gate rows, then up rows
+                self.down.weight.uniform_(-1.0 / math.sqrt(hidden), 1.0 / math.sqrt(hidden), generator=g)
+            return
+        self.gate = make_linear(d_model, hidden, use_fp4, device)
+        self.up = make_linear(d_model, hidden, use_fp4, device)
+        self.down = make_linear(hidden, d_model, use_fp4, device)
         with torch.no_grad():
             for lin in (self.gate, self.up, self.down):
                 bound = 1.0 / math.sqrt(lin.weight.shape[1])          # kaiming_uniform_(a=sqrt(5))
@@ -36,6 +51,12 @@ class SwiGLUFFN(nn.Module):
         # FP4Linear.forward(amax_signs=) and linear.hint_grad_amax(signs=).
 
     def forward(self, x):
+        if self.fuse_gate_up:
+            gu = self.gate_up(x)
+            if gu.dtype == torch.bfloat16 and gu.is_cuda:
+                h, h_max = swiglu_packed(gu, self.gate_up.signs if gu.numel() // gu.shape[-1] % 16 == 0 else None)
+                return self.down(h, amax=h_max, amax_signs=self.gate_up.signs)
+            return self.down(F.silu(gu[..., :self.hidden]) * gu[..., self.hidden:])
         g, u = self.gate(x), self.up(x)
         if self.fused and isinstance(self.down, FP4Linear) and g.dtype == torch.bfloat16 and g.is_cuda:
             h, h_max = swiglu(g, u, self.gate.signs if g.numel() // g.shape[-1] % 16 == 0 else None)

@@ -103,7 +103,10 @@ class FP4LinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, H, signs, wq_K, wq_N, amax_reduce=None, sharded=(False, False), x_amax=None,
-                x_amax_rht=True):
+                x_amax_rht=True, dx_reduce=None):
+        # dx_reduce: optional callable(dx) -> handle with .wait(): starts the sum of the input gradient
+        # over a tensor-parallel group right after the dgrad GEMM, so that it runs beside the wgrad
+        # quantizations and GEMM; the handle is waited for before the backward returns
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         x_sharded, y_sharded = sharded[0], sharded[1]  # is the K dim / the N dim split across ranks?
@@ -126,6 +129,7 @@ class FP4LinearFn(torch.autograd.Function):
         ctx.H, ctx.signs, ctx.xshape, ctx.wq_N = H, signs, x.shape, wq_N
         ctx.amax_reduce, ctx.sharded, ctx.x_amax = amax_reduce, sharded, x_amax
         ctx.x_amax_rht = bool(x_amax_rht)        # False: the Hadamard maximum came from another sign vector
+        ctx.dx_reduce = dx_reduce
         return y.reshape(*x.shape[:-1], w.shape[0]).to(x.dtype)
 
     @staticmethod
@@ -160,13 +164,16 @@ class FP4LinearFn(torch.autograd.Function):
             if wq_N is None:
                 wq_N = _quant(w, red, transpose=True)
             dx = nvfp4_mm(gq, wq_N.t(), torch.bfloat16).reshape(ctx.xshape).to(gy.dtype)
+        pending = ctx.dx_reduce(dx) if (dx is not None and ctx.dx_reduce is not None) else None
         if ctx.needs_input_grad[1]:
             # wgrad: dW = dY^T @ X, contraction over tokens; Hadamard on both, SR on the gradient
             gtq = _quant(gy2, None if g_amax_rht is not None else g_red, stochastic=True, rht=True, H=H, signs=signs,
                          transpose=True, amax=g_amax_rht, counter=ctr_cols)
             xtq = _quant(x2, xt_red, rht=True, H=H, signs=signs, transpose=True, amax=x_amax_rht)
             dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
-        return dx, dw, None, None, None, None, None, None, None, None
+        if pending is not None:
+            pending.wait()
+        return dx, dw, None, None, None, None, None, None, None, None, None
 
 
 def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False, amax=None, counter=None):

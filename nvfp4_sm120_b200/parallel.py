@@ -102,17 +102,17 @@ class _ParallelLinearBase(nn.Module):
             self._cache = None
             self.H = self.signs = None
 
-    def _call(self, x, sharded, x_amax=None, x_amax_signs=None):
+    def _call(self, x, sharded, x_amax=None, x_amax_signs=None, dx_reduce=None):
         """x_amax: this rank's maxima of x from a fused producer (swiglu.SwiGLUFn), FP4 path only;
-        x_amax_signs: the sign vector its Hadamard maximum was computed with."""
+        x_amax_signs: the sign vector its Hadamard maximum was computed with; dx_reduce: see FP4LinearFn."""
         wq_K = wq_N = None
         if self._cache is not None:
             wq_K, wq_N = self._cache.get(self.weight, self.amax_reduce)
-        if x_amax is not None and self.linear_fn is _fp4_linear_fn:
+        if (x_amax is not None or dx_reduce is not None) and self.linear_fn is _fp4_linear_fn:
             from .linear import FP4LinearFn, _same_signs
             rht_ok = x_amax_signs is None or _same_signs(x_amax_signs, self.signs)
             return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, self.amax_reduce, sharded, x_amax,
-                                     rht_ok)
+                                     rht_ok, dx_reduce)
         return self.linear_fn(x, self.weight, self.H, self.signs, wq_K, wq_N, self.amax_reduce, sharded)
 
 
@@ -120,14 +120,24 @@ class ColumnParallelFP4Linear(_ParallelLinearBase):
     """y_local[*, out/p] = x @ W_local^T.  x is replicated; the output and its gradient are split
     along the feature dim, so their amax is reduced; dX is summed over the group."""
 
-    def forward(self, x, copied=False):
+    def forward(self, x, copied=False, overlap_dx=False, contiguous_shard=True):
         """copied: x already went through the group's copy (the caller feeds several column-parallel
-        layers from one copy so that their input gradients are summed locally and all-reduced once)."""
+        layers from one copy so that their input gradients are summed locally and all-reduced once).
+        overlap_dx (FP4 path): no copy node; the layer itself starts the all-reduce of its input
+        gradient right after its dgrad GEMM and waits for it after its wgrad GEMM.
+        contiguous_shard: the shard is rows [rank n/p, (rank+1) n/p) of the whole weight, so its output
+        gradient can draw the whole tensor's stochastic-rounding bits (False for packed gate|up shards)."""
+        place = None
+        if contiguous_shard and dist.is_available() and dist.is_initialized():
+            place = (dist.get_rank(self.group), dist.get_world_size(self.group))
+        if overlap_dx and self.linear_fn is _fp4_linear_fn:
+            group = self.group
+
+            def start_sum(dx):
+                return dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=group, async_op=True)
+            return self._call(x, (False, True, place), dx_reduce=start_sum)
         if not copied:
             x = _CopyToGroup.apply(x, self.group)
-        place = None
-        if dist.is_available() and dist.is_initialized():
-            place = (dist.get_rank(self.group), dist.get_world_size(self.group))
         return self._call(x, (False, True, place))
 
 
@@ -145,20 +155,33 @@ class TensorParallelSwiGLU(nn.Module):
     (benchmark config 4: d 4096, h 14336).  Built from this rank's shards: gate/up [h/p, d], down [d, h/p];
     `from_full` slices them out of the unsharded [h, d], [h, d], [d, h] weights."""
 
-    def __init__(self, gate_shard, up_shard, down_shard, group=None, linear_fn=None, device="cuda"):
+    def __init__(self, gate_shard, up_shard, down_shard, group=None, linear_fn=None, device="cuda", fuse_gate_up=False):
+        """fuse_gate_up (FP4 path): this rank's gate and up shards as ONE [2 h/p, d] projection: x is
+        quantized once per layout, one dgrad GEMM over K = 2 h/p whose all-reduce runs beside the
+        wgrad GEMM, and the SwiGLU kernels work on the packed [tokens, 2 h/p] tensors in place."""
         super().__init__()
-        self.gate = ColumnParallelFP4Linear(gate_shard, group, linear_fn, device)
-        self.up = ColumnParallelFP4Linear(up_shard, group, linear_fn, device)
+        self.fuse_gate_up = bool(fuse_gate_up and linear_fn is None)
+        if self.fuse_gate_up:
+            self.gate_up = ColumnParallelFP4Linear(torch.cat([gate_shard, up_shard], 0), group, linear_fn, device)
+        else:
+            self.gate = ColumnParallelFP4Linear(gate_shard, group, linear_fn, device)
+            self.up = ColumnParallelFP4Linear(up_shard, group, linear_fn, device)
         self.down = RowParallelFP4Linear(down_shard, group, linear_fn, device)
 
     @classmethod
-    def from_full(cls, full_gate, full_up, full_down, group=None, linear_fn=None, device="cuda"):
+    def from_full(cls, full_gate, full_up, full_down, group=None, linear_fn=None, device="cuda", fuse_gate_up=False):
         rank = dist.get_rank(group) if dist.is_initialized() else 0
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         return cls(shard_rows(full_gate, rank, world), shard_rows(full_up, rank, world),
-                   shard_cols(full_down, rank, world), group, linear_fn, device)
+                   shard_cols(full_down, rank, world), group, linear_fn, device, fuse_gate_up)
 
     def forward(self, x):
+        if self.fuse_gate_up:
+            from .swiglu import swiglu_packed
+            gu = self.gate_up(x, overlap_dx=True, contiguous_shard=False)
+            tokens = gu.numel() // gu.shape[-1]
+            h, h_max = swiglu_packed(gu, self.gate_up.signs if tokens % 16 == 0 else None)
+            return self.down(h, amax=h_max, amax_signs=self.gate_up.signs)
         # one copy-to-group for both projections: autograd adds gate's and up's input gradients
         # locally and the sum crosses the links once
         xc = _CopyToGroup.apply(x, self.gate.group)

@@ -64,6 +64,62 @@ class SwiGLUFn(torch.autograd.Function):
         return dg, du, None
 
 
+class SwiGLUPackedFn(torch.autograd.Function):
+    """gu [*, 2H] = gate | up side by side (the output of one fused projection) -> (h [*, H], maxima):
+    SwiGLUFn without the split: the kernels read the two halves in place (row stride 2H), and the
+    backward writes dgate | dup into ONE [*, 2H] tensor, the gradient of the fused projection, and
+    hints its maxima (the larger of the two halves') to that projection."""
+
+    @staticmethod
+    def forward(ctx, gu, signs):
+        if gu.dtype != torch.bfloat16 or gu.shape[-1] % 16 != 0:
+            raise ValueError("fused SwiGLU takes a bf16 tensor whose last dimension is 2H, H a multiple of 8")
+        gu2 = _rows(gu).contiguous()
+        rows, two_h = gu2.shape
+        hid = two_h // 2
+        use_rht = signs is not None and rows % 16 == 0
+        sg = _signs(signs, gu.device) if use_rht else None
+        h = torch.empty((rows, hid), dtype=torch.bfloat16, device=gu.device)
+        maxima = torch.empty(2, dtype=torch.float32, device=gu.device)
+        g_ptr, u_ptr = gu2.data_ptr(), gu2.data_ptr() + 2 * hid
+        with torch.cuda.device(gu2.device):           # the C side launches on the current device
+            code = _lib.lib().nvfp4_swiglu_fwd_bf16(g_ptr, u_ptr, rows, hid, two_h, h.data_ptr(), hid,
+                                                    sg.data_ptr() if use_rht else None, maxima.data_ptr(), 1,
+                                                    _stream(gu2.device))
+        _lib.check(code, "nvfp4_swiglu_fwd_bf16")
+        ctx.save_for_backward(gu2)
+        ctx.sg, ctx.use_rht, ctx.shape, ctx.signs_in = sg, use_rht, gu.shape, signs
+        ctx.mark_non_differentiable(maxima)
+        return h.reshape(*gu.shape[:-1], hid), maxima
+
+    @staticmethod
+    def backward(ctx, dh, _dmax):
+        (gu2,) = ctx.saved_tensors
+        rows, two_h = gu2.shape
+        hid = two_h // 2
+        d2 = _rows(dh)
+        if d2.dtype != torch.bfloat16:
+            d2 = d2.to(torch.bfloat16)
+        d2 = d2.contiguous()
+        dgu = torch.empty_like(gu2)
+        maxima = torch.empty(4, dtype=torch.float32, device=gu2.device)
+        with torch.cuda.device(gu2.device):
+            code = _lib.lib().nvfp4_swiglu_bwd_strided_bf16(
+                gu2.data_ptr(), gu2.data_ptr() + 2 * hid, d2.data_ptr(), rows, hid, two_h, hid,
+                dgu.data_ptr(), dgu.data_ptr() + 2 * hid, two_h, ctx.sg.data_ptr() if ctx.use_rht else None,
+                maxima.data_ptr(), 1, _stream(gu2.device))
+        _lib.check(code, "nvfp4_swiglu_bwd_strided_bf16")
+        both = torch.maximum(maxima[0:2], maxima[2:4])            # maxima of dgate | dup as one tensor
+        dgu = dgu.reshape(ctx.shape)
+        _linear.hint_grad_amax(dgu, both, ctx.use_rht, ctx.signs_in)
+        return dgu, None
+
+
+def swiglu_packed(gu, signs=None):
+    """h = silu(gu[..., :H]) * gu[..., H:] and the maxima of h (see SwiGLUPackedFn)."""
+    return SwiGLUPackedFn.apply(gu, signs)
+
+
 def swiglu(g, u, signs=None):
     """h = silu(g) * u and the maxima of h (see SwiGLUFn)."""
     return SwiGLUFn.apply(g, u, signs)

@@ -216,3 +216,53 @@ def test_hadamard_hint_is_dropped_for_another_sign_vector(Q):
     quant._SEED[0] = 77
     lin(x).sum().backward()
     assert torch.equal(lin.weight.grad, g1)
+
+
+def test_packed_gate_up_kernels_match_the_split_ones(Q):
+    """SwiGLU on a packed [tokens, 2H] gate|up tensor (the output of one fused projection) gives the
+    bytes of the split form, forward and backward, and hints the maxima of the packed gradient."""
+    from nvfp4_sm120_b200 import linear, quant
+    from nvfp4_sm120_b200.swiglu import swiglu, swiglu_packed
+    from oracle import nvfp4_oracle as O
+    gen = torch.Generator(device="cuda").manual_seed(12)
+    T, H = 256, 384
+    gu = (torch.randn(T, 2 * H, device="cuda", generator=gen) * 1.5).to(torch.bfloat16).requires_grad_(True)
+    dh = torch.randn(T, H, device="cuda", generator=gen).to(torch.bfloat16)
+    signs = O.signs_from_seed(3).cuda()
+    g = gu.detach()[:, :H].contiguous().requires_grad_(True)
+    u = gu.detach()[:, H:].contiguous().requires_grad_(True)
+    linear._GRAD_AMAX.clear()
+    h1, m1 = swiglu(g, u, signs)
+    dg, du = torch.autograd.grad(h1, [g, u], grad_outputs=dh)
+    linear._GRAD_AMAX.clear()
+    h2, m2 = swiglu_packed(gu, signs)
+    (dgu,) = torch.autograd.grad(h2, [gu], grad_outputs=dh)
+    assert torch.equal(h1, h2) and torch.equal(_bits(m1), _bits(m2))
+    assert torch.equal(dgu[:, :H], dg) and torch.equal(dgu[:, H:], du)
+    plain, rht = linear._take_grad_amax(dgu, signs)
+    assert torch.equal(_bits(plain), _bits(quant.tensor_amax(dgu)))
+    assert torch.equal(_bits(rht), _bits(quant.tensor_amax(dgu, rht=True, signs=signs, transpose=True)))
+
+
+def test_ffn_with_fused_gate_up_projection(Q):
+    """The FFN with gate and up as one [2h, d] projection: same initial weights as the three-linear
+    form, output and gradients at the quantisation level of the exact block (the per-tensor scale of
+    the fused weight spans both halves, so the bytes are not those of two separate linears)."""
+    from nvfp4_sm120_b200.ffn import SwiGLUFFN
+    d, h, T = 256, 512, 128
+    a = SwiGLUFFN(d, h, use_fp4=True, seed=4)
+    b = SwiGLUFFN(d, h, use_fp4=True, seed=4, fuse_gate_up=True)
+    assert torch.equal(b.gate_up.weight[:h], a.gate.weight) and torch.equal(b.gate_up.weight[h:], a.up.weight)
+    assert torch.equal(b.down.weight, a.down.weight)
+    x = torch.randn(T, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    gy = torch.randn(T, d, device="cuda", dtype=torch.bfloat16)
+    y = b(x)
+    gx, gw = torch.autograd.grad(y, [x, b.gate_up.weight], grad_outputs=gy)
+    xe = x.detach().float().requires_grad_(True)
+    wg, wu, wd = (t.detach().float().requires_grad_(True) for t in (a.gate.weight, a.up.weight, a.down.weight))
+    ye = (F.silu(xe @ wg.t()) * (xe @ wu.t())) @ wd.t()
+    ex, eg, eu = torch.autograd.grad(ye, [xe, wg, wu], grad_outputs=gy.float())
+    rel = lambda p, q: ((p.float() - q).norm() / q.norm()).item()
+    assert rel(y, ye) < 0.25 and rel(gx, ex) < 0.35
+    assert rel(gw[:h], eg) < 0.35 and rel(gw[h:], eu) < 0.35
+    assert Q.gemm_status() == 0
