@@ -35,7 +35,8 @@ class SwiGLUFFN(nn.Module):
             self.down = make_linear(hidden, d_model, use_fp4, device)
             with torch.no_grad():
                 bound = 1.0 / math.sqrt(d_model)
-                self.gate_up.weight.uniform_(-bound, bound, generator=g)       # gate rows, then up rows
+                self.gate_up.weight[:hidden].uniform_(-bound, bound, generator=g)      # gate rows ...
+                self.gate_up.weight[hidden:].uniform_(-bound, bound, generator=g)      # ... then up rows
                 self.down.weight.uniform_(-1.0 / math.sqrt(hidden), 1.0 / math.sqrt(hidden), generator=g)
             return
         self.gate = make_linear(d_model, hidden, use_fp4, device)
