@@ -211,9 +211,8 @@ int nvfp4_gemm_fp4out(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pt
 
 /*
  * Kernel choice of nvfp4_gemm for this process: 0 = automatic (the default), 1 = always the
- * one-CTA 128x256 kernel, 2 = always the persistent two-CTA kernel with 256x256 tiles, 3 = always
- * the persistent two-CTA kernel with 256x384 tiles.  For tuning and tests; results are the same to
- * rounding of the accumulation order.  No counterpart in the reference.
+ * one-CTA 128x256 kernel, 2 = always the persistent two-CTA 256x256 kernel.  For tuning and tests;
+ * results are the same to rounding of the accumulation order.  No counterpart in the reference.
  */
 int nvfp4_gemm_set_mode(int mode);
 

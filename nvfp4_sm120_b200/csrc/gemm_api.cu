@@ -5,10 +5,6 @@ namespace nvfp4 { namespace gemm3 {
 int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const gemm::Params& p,
                 cudaStream_t stream);
 }}
-namespace nvfp4 { namespace gemm4 {
-int launch_wide(const CUtensorMap& map_a, const CUtensorMap& map_b1, const CUtensorMap& map_b2, const CUtensorMap& map_d,
-                const gemm::Params& p, cudaStream_t stream);
-}}
 namespace nvfp4 { namespace gemm {
 int launch_1cta(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_d, const Params& p,
                 cudaStream_t stream);
@@ -27,7 +23,7 @@ void set_test_hooks(unsigned long long wait_ns, int drop_arrival) {
 }
 }}
 extern "C" int nvfp4_gemm_set_mode(int mode) {
-  if (mode < 0 || mode > 3) return NVFP4_E_MODE;
+  if (mode < 0 || mode > 2) return NVFP4_E_MODE;
   g_gemm_mode.store(mode, std::memory_order_relaxed);
   return NVFP4_OK;
 }
@@ -62,7 +58,7 @@ static int gemm_any(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
   const bool want_split = out_dtype == NVFP4_OUT_F32 && tiles_1cta <= 74 && slices >= 16;
   const int forced = g_gemm_mode.load(std::memory_order_relaxed);
   const int mode = forced != 0 ? forced : ((M > 128 && !want_split) ? 2 : 1);
-  const bool pair = mode >= 2;
+  const bool pair = mode == 2;
   CUtensorMap map_a, map_b;
   if (!make_operand_map(&map_a, a_q, M, K, 128) || !make_operand_map(&map_b, b_q, N, K, pair ? 128 : 256))
     return NVFP4_E_DRIVER;
@@ -91,11 +87,6 @@ static int gemm_any(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
   if (p.splits == 1 && !fp4_out && (ldd * (p.out_f32 ? 4 : 2)) % 16 == 0) {
     if (!make_output_map(&map_d, d, M, N, ldd, p.out_f32 != 0)) return NVFP4_E_DRIVER;
     p.tma_store = 1;
-  }
-  if (mode == 3) {
-    CUtensorMap map_b2;
-    if (!make_operand_map(&map_b2, b_q, N, K, 64)) return NVFP4_E_DRIVER;
-    return nvfp4::gemm4::launch_wide(map_a, map_b, map_b2, map_d, p, stream);
   }
   return pair ? nvfp4::gemm3::launch_pair(map_a, map_b, map_d, p, stream) : launch_1cta(map_a, map_b, map_d, p, stream);
 }

@@ -29,7 +29,7 @@ def main():
     ap.add_argument("--heads", type=int, default=12, help="block: attention heads (sequence length 1024)")
     ap.add_argument("--bf16", action="store_true", help="ffn: bf16 nn.Linear comparator instead of FP4Linear")
     ap.add_argument("--iters", type=int, default=3)
-    ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 one-CTA kernel, 2 / 3 persistent two-CTA kernel with 256x256 / 256x384 tiles")
+    ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 one-CTA kernel, 2 persistent two-CTA kernel")
     a = ap.parse_args()
     dev = torch.device("cuda", 0)
     from nvfp4_sm120_b200 import _lib

@@ -86,9 +86,9 @@ def test_static_entry_point_reports_a_give_up(L):
     assert L.nvfp4_quantize_static_status(None, 0, None) == -1
 
 
-@pytest.mark.parametrize("mode", [1, 2, 3])
+@pytest.mark.parametrize("mode", [1, 2])
 def test_gemm_wait_gives_up_reports_and_recovers(L, mode):
-    """mode 1: one-CTA kernel, modes 2 and 3: the persistent pair kernels (256 x 256 and 256 x 384 tiles).  The scale-factor warps never announce
+    """mode 1: one-CTA kernel, mode 2: persistent pair kernel.  The scale-factor warps never announce
     K slice 0; every role leaves its loop through a bounded wait, tensor memory is freed, the status
     word carries the code of the first wait that gave up, and the next launch is exact."""
     import nvfp4_sm120_b200 as Q

@@ -36,11 +36,11 @@ def test_gemm_fp32_out_matches_dequant_matmul(Q, mnk):
     assert torch.allclose(got, ref, rtol=2e-3, atol=2e-3 * ref.abs().max().item())
 
 
-@pytest.mark.parametrize("mode", [2, 3])
+@pytest.mark.parametrize("mode", [2])
 @pytest.mark.parametrize("mnk", [(256, 512, 512), (130, 200, 320), (384, 768, 2048), (48, 80, 64), (1024, 1024, 4096)])
 def test_two_cta_kernel_matches(Q, mnk, mode):
-    """The persistent cta_group::2 kernels (mode 2: 256 x 256 tiles, mode 3: 256 x 384 tiles) give the
-    one-CTA kernel's result and meet the tolerance, in fp32 and in bf16."""
+    """The persistent cta_group::2 kernel (mode 2) gives the one-CTA kernel's result and meets the
+    tolerance, in fp32 and in bf16."""
     from nvfp4_sm120_b200 import _lib
     m, n, k = mnk
     qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 12).cuda())
@@ -63,7 +63,7 @@ def test_two_cta_kernel_matches(Q, mnk, mode):
     assert torch.allclose(one_bf.float(), one, rtol=2.0 ** -7, atol=1e-5 * ref.abs().max().item())
 
 
-@pytest.mark.parametrize("mode", [1, 2, 3])
+@pytest.mark.parametrize("mode", [1, 2])
 def test_many_tiles_per_cluster_and_strided_output(Q, mode):
     """More tiles than SM pairs (the persistent kernel loops), ragged M and N, and an output whose
     row pitch is larger than N (TMA-store epilogue with a pitch) or not a multiple of 16 bytes
@@ -194,7 +194,7 @@ def test_standalone_c_driver_verifies():
         assert "Disposition: Passed" in res.stdout
 
 
-@pytest.mark.parametrize("mode", [1, 2, 3])
+@pytest.mark.parametrize("mode", [1, 2])
 @pytest.mark.parametrize("mnk", [(256, 512, 512), (130, 208, 320), (1024, 768, 2048)])
 def test_fp4_output_epilogue_equals_quantizing_the_bf16_output(Q, mnk, mode):
     """The NVFP4-output epilogue (for chained GEMMs; the reference's CUTLASS example has the same
