@@ -28,6 +28,7 @@ def main():
     ap.add_argument("--micro", type=int, default=8)
     ap.add_argument("--heads", type=int, default=12, help="block: attention heads (sequence length 1024)")
     ap.add_argument("--bf16", action="store_true", help="ffn: bf16 nn.Linear comparator instead of FP4Linear")
+    ap.add_argument("--fuse-gate-up", action="store_true", help="ffn: one [2h, d] gate|up projection")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--gemm-mode", type=int, default=0, help="0 auto, 1 one-CTA kernel, 2 persistent two-CTA kernel")
     a = ap.parse_args()
@@ -39,7 +40,7 @@ def main():
     if a.case == "ffn":
         from nvfp4_sm120_b200.ffn import SwiGLUFFN, ffn_flops
         Q.set_amortize(True)
-        m = SwiGLUFFN(a.d, a.h, use_fp4=not a.bf16, device=dev, seed=4)
+        m = SwiGLUFFN(a.d, a.h, use_fp4=not a.bf16, device=dev, seed=4, fuse_gate_up=a.fuse_gate_up)
         if a.bf16:
             m = m.to(torch.bfloat16)
         xs = [torch.randn(a.tokens, a.d, device=dev, dtype=torch.bfloat16, generator=g).requires_grad_(True)
