@@ -193,6 +193,21 @@ int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
                int32_t* status, void* stream);
 
 /*
+ * nvfp4_gemm that also leaves max|D| in *d_amax_out (fp32 device word; the call zeroes it on the
+ * stream first): the maximum over the stored output after its rounding to the output type, i.e.
+ * what nvfp4_amax_bf16 would find by reading D again.  A quantizer that takes D next
+ * (nvfp4_quantize_fused_bf16 with this word as amax_in) then needs one pass, not two.  The K split
+ * of small fp32 outputs is not used with this entry point.
+ * Replaces the `tf.abs().amax()` pass of quant_nvfp4 (nvfp4_gemm.py:34-36) over a GEMM output, e.g.
+ * between `up` and `down` at nvfp4_train.py:111-123; the quantization overhead it removes is the one
+ * the reference names at README.md:80-83.
+ */
+int nvfp4_gemm_amax(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
+                    const uint8_t* b_q, const uint8_t* b_sf, const float* b_pts,
+                    void* d, int out_dtype, int64_t M, int64_t N, int64_t K, int64_t ldd,
+                    float* d_amax_out, int32_t* status, void* stream);
+
+/*
  * The same GEMM with an NVFP4 OUTPUT for chained GEMMs: every output row is rounded to bf16 and
  * quantized in blocks of 16 along N (round to nearest) inside the epilogue, with the per-tensor
  * maximum *d_amax supplied by the caller (a value known from the previous step or a bound; elements
@@ -262,6 +277,24 @@ int nvfp4_relu2_fwd_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld_i
 int nvfp4_relu2_bwd_bf16(const void* x, const void* dout, int64_t rows, int64_t cols, int64_t ld_in,
                          void* dx, int64_t ld_out, const float* signs16, float* maxima2, int zero_first,
                          void* stream);
+
+/*
+ * RMSNorm as a producer for the quantizer: h = x * rsqrt(mean(x^2, row) + eps) * weight, written once as
+ * bf16 [rows, cols] (contiguous), with rstd[rows] for the backward and maxima2 = {max|h|,
+ * max|RHT_rows(h)|} of the ROUNDED result (the second only if signs16 is given; rows % 16 == 0 then).
+ * Every NVFP4 quantization of h that follows (the q, k, v / up projections in both layouts) is then one
+ * pass with the maximum given.  x is fp32 (x_is_f32 != 0) or bf16, contiguous; cols % 8 == 0; pointers
+ * 16-byte aligned.  Backward: dx (in x's type) and dweight (fp32 [cols], zeroed first if zero_first,
+ * accumulated with atomics) from g = dL/dh (bf16, or fp32 when g_is_f32 != 0).
+ * Call site in the reference: nn.RMSNorm n1 / n2 in front of the FP4 projections
+ * (nvfp4_train.py:105,114-122); there each FP4Linear searches the maximum of the same tensor again.
+ */
+int nvfp4_rmsnorm_fwd(const void* x, int x_is_f32, const float* weight, int64_t rows, int64_t cols, float eps,
+                      void* h_bf16, float* rstd, const float* signs16, float* maxima2, int zero_first,
+                      void* stream);
+int nvfp4_rmsnorm_bwd(const void* x, int x_is_f32, const float* weight, const float* rstd, const void* g,
+                      int g_is_f32, int64_t rows, int64_t cols, void* dx, float* dweight, int zero_first,
+                      void* stream);
 
 /*
  * Test hooks of the bounded waits, process-wide, for the launches that follow.  Every spin inside

@@ -47,11 +47,18 @@ _SIGS = {
                                         _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nvfp4_relu2_bwd_bf16": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p,
                                         _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "nvfp4_rmsnorm_fwd": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_float,
+                                     _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "nvfp4_rmsnorm_bwd": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int,
+                                     _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nvfp4_gemm_set_mode": (_c.c_int, [_c.c_int]),
     "nvfp4_gemm_fp4out": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                      _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                      _c.c_void_p, _c.c_void_p, _c.c_void_p]),
     "nvfp4_test_hooks": (_c.c_int, [_c.c_uint64, _c.c_int, _c.c_int]),
+    "nvfp4_gemm_amax": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                   _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
+                                   _c.c_void_p, _c.c_void_p, _c.c_void_p]),
     "nvfp4_gemm": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                               _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
                               _c.c_void_p, _c.c_void_p]),

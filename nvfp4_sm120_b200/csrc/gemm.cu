@@ -202,6 +202,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       if (!ok) raise(abort_flag, p.status, kErrEpilogueWait);
     }
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    uint32_t mbits = 0u;
     if (ok) {
       tc_fence_after();
       const float alpha = __ldg(p.a_pts) * __ldg(p.b_pts);
@@ -209,7 +210,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
       if (p.tma_store) {
         // every MMA has finished and every TMA load has landed, so the stages are free: 32 KiB per warp
-        drain_through_tma(p, &map_d, taddr, smem + (warp - 2) * 32768, m0 + quad * 32, n0, 0, kTileN, alpha, lane);
+        drain_through_tma(p, &map_d, taddr, smem + (warp - 2) * 32768, m0 + quad * 32, n0, 0, kTileN, alpha, lane,
+                          mbits);
       } else {
 #pragma unroll 1
         for (int c0 = 0; c0 < kTileN; c0 += 32) {
@@ -217,10 +219,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           uint32_t r[32];
           tc_ld_32x32b_x32(taddr + c0, r);
           tc_wait_ld();
+          if (p.d_amax_out != nullptr) track_amax(p, r, alpha, row, n0 + c0, mbits);
           if (row < p.M) store_row_chunk(p, row, n0 + c0, r, alpha);
         }
       }
     }
+    flush_amax(p, mbits, lane);
   }
   tc_fence_before();
   __syncthreads();

@@ -43,7 +43,8 @@ int launch_pts_from_amax(const float* amax, float* pts, cudaStream_t stream) {
 
 static int gemm_any(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
                     const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
-                    int64_t K, int64_t ldd, uint8_t* d_sf, const float* d_amax, int32_t* status, void* stream_) {
+                    int64_t K, int64_t ldd, uint8_t* d_sf, const float* d_amax, float* d_amax_out, int32_t* status,
+                    void* stream_) {
   using namespace nvfp4::gemm;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const bool fp4_out = d_sf != nullptr;
@@ -55,7 +56,12 @@ static int gemm_any(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
   if (mis(a_q, 16) || mis(b_q, 16) || mis(a_sf, 16) || mis(b_sf, 16) || mis(d, 16)) return NVFP4_E_ALIGN;
   // split K (one-CTA kernel only, see below) when a small fp32 output would leave most SMs idle
   const int64_t tiles_1cta = ((N + 255) / 256) * ((M + 127) / 128), slices = (K + 255) / 256;
-  const bool want_split = out_dtype == NVFP4_OUT_F32 && tiles_1cta <= 74 && slices >= 16;
+  // (partial sums have no maximum of their own: no split when the caller wants max|D|)
+  const bool want_split = out_dtype == NVFP4_OUT_F32 && tiles_1cta <= 74 && slices >= 16 && d_amax_out == nullptr;
+  if (d_amax_out != nullptr) {
+    if (fp4_out) return NVFP4_E_MODE;
+    if (cudaMemsetAsync(d_amax_out, 0, sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
+  }
   const int forced = g_gemm_mode.load(std::memory_order_relaxed);
   const int mode = forced != 0 ? forced : ((M > 128 && !want_split) ? 2 : 1);
   const bool pair = mode == 2;
@@ -64,7 +70,7 @@ static int gemm_any(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
     return NVFP4_E_DRIVER;
   Params p{a_sf, b_sf, a_pts, b_pts, d, M, N, K, ldd, out_dtype == NVFP4_OUT_F32 ? 1 : 0, status, 1, 0,
            g_gemm_wait_ns.load(std::memory_order_relaxed), g_gemm_drop_arrival.load(std::memory_order_relaxed),
-           d_sf, d_amax, fp4_out ? 1 : 0};
+           d_sf, d_amax, fp4_out ? 1 : 0, d_amax_out};
   // Split K when a small fp32 output (the weight gradient: few tiles, K = tokens) would leave most SMs
   // idle: the CTAs of a tile add their partial sums into the zeroed output.  Summation order then
   // varies from run to run in the last bits, so it is used only where it pays: fewer tiles than half
@@ -94,7 +100,16 @@ static int gemm_any(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts,
 extern "C" int nvfp4_gemm(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
                           const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
                           int64_t K, int64_t ldd, int32_t* status, void* stream_) {
-  return gemm_any(a_q, a_sf, a_pts, b_q, b_sf, b_pts, d, out_dtype, M, N, K, ldd, nullptr, nullptr, status, stream_);
+  return gemm_any(a_q, a_sf, a_pts, b_q, b_sf, b_pts, d, out_dtype, M, N, K, ldd, nullptr, nullptr, nullptr, status,
+                  stream_);
+}
+
+extern "C" int nvfp4_gemm_amax(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
+                               const uint8_t* b_sf, const float* b_pts, void* d, int out_dtype, int64_t M, int64_t N,
+                               int64_t K, int64_t ldd, float* d_amax_out, int32_t* status, void* stream_) {
+  if (!d_amax_out) return NVFP4_E_NULL;
+  return gemm_any(a_q, a_sf, a_pts, b_q, b_sf, b_pts, d, out_dtype, M, N, K, ldd, nullptr, nullptr, d_amax_out, status,
+                  stream_);
 }
 
 extern "C" int nvfp4_gemm_fp4out(const uint8_t* a_q, const uint8_t* a_sf, const float* a_pts, const uint8_t* b_q,
@@ -108,7 +123,8 @@ extern "C" int nvfp4_gemm_fp4out(const uint8_t* a_q, const uint8_t* a_sf, const 
   // padding of the tiled scale buffer reads as zero; the per-tensor scale is the given maximum / 2688
   const int64_t sm = (M + 127) / 128 * 128, sk = (N / 16 + 3) / 4 * 4;
   if ((sm != M || sk != N / 16) && cudaMemsetAsync(d_sf, 0, (size_t)(sm * sk), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
-  const int rc = gemm_any(a_q, a_sf, a_pts, b_q, b_sf, b_pts, d_q, NVFP4_OUT_BF16, M, N, K, N, d_sf, d_amax, status, stream_);
+  const int rc = gemm_any(a_q, a_sf, a_pts, b_q, b_sf, b_pts, d_q, NVFP4_OUT_BF16, M, N, K, N, d_sf, d_amax, nullptr, status,
+                          stream_);
   if (rc != NVFP4_OK) return rc;
   return nvfp4::gemm::launch_pts_from_amax(d_amax, d_pts, stream);
 }

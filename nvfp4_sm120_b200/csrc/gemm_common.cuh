@@ -153,6 +153,9 @@ struct Params {
   uint8_t* d_sf;                      // swizzled E4M3 scales of the [M, N] operand
   const float* d_amax;
   int out_fp4;
+  // optional: the kernel leaves max|D| over the stored output (after its rounding to the output type) in
+  // this zeroed fp32 word, so that a quantizer reading D next needs no pass of its own to find it
+  float* d_amax_out;
 };
 
 __device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status, int code) {
@@ -160,6 +163,29 @@ __device__ __forceinline__ void raise(volatile int* abort_flag, int32_t* status,
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+
+// Running maximum of |D| over the elements this thread stores, kept as the bit pattern of a
+// non-negative float (unsigned order = numeric order, and a NaN stays on top).  32 accumulator columns
+// of one output row per call; rows and columns outside the matrix do not count.
+__device__ __forceinline__ void track_amax(const Params& p, const uint32_t (&r)[32], float alpha, int64_t row,
+                                           int64_t col, uint32_t& mbits) {
+  if (row >= p.M) return;
+  const int64_t left = p.N - col;
+  const int n = left < 32 ? (int)left : 32;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    float v = __uint_as_float(r[j]) * alpha;
+    if (!p.out_f32) v = __bfloat162float(__float2bfloat16_rn(v));
+    const uint32_t b = __float_as_uint(v) & 0x7fffffffu;
+    if (j < n) mbits = max(mbits, b);
+  }
+}
+// one atomic per warp and kernel
+__device__ __forceinline__ void flush_amax(const Params& p, uint32_t mbits, int lane) {
+  if (p.d_amax_out == nullptr) return;
+  const uint32_t m = __reduce_max_sync(0xffffffffu, mbits);
+  if (lane == 0 && m != 0u) atomicMax(reinterpret_cast<unsigned int*>(p.d_amax_out), m);
+}
 
 // 32 consecutive accumulator columns of one output row: scale by alpha, convert, store
 // (vector stores when the chunk is whole and the leading dimension allows it).
@@ -273,7 +299,7 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t sr
 // bf16 or 32 fp32 columns, 1024-byte aligned, not reused (so nothing waits until the end).
 __device__ __forceinline__ void drain_through_tma(const Params& p, const CUtensorMap* map_d, uint32_t taddr,
                                                   uint8_t* buf, int64_t row0, int64_t n0, int c_begin, int c_end,
-                                                  float alpha, int lane) {
+                                                  float alpha, int lane, uint32_t& mbits) {
   if (row0 >= p.M) return;                               // padded rows of a pair: nothing to write
   const uint32_t sw = (uint32_t)lane & 7u;
   int box = 0;
@@ -283,6 +309,7 @@ __device__ __forceinline__ void drain_through_tma(const Params& p, const CUtenso
     uint32_t r[32];
     tc_ld_32x32b_x32(taddr + c0, r);
     tc_wait_ld();
+    if (p.d_amax_out != nullptr) track_amax(p, r, alpha, row0 + lane, n0 + c0, mbits);
     uint8_t* rowp = buf + box * 4096 + lane * 128;
     bool box_done = true;
     int x = (int)(n0 + c0);

@@ -306,6 +306,7 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
     const float alpha = __ldg(p.a_pts) * __ldg(p.b_pts);
     const uint32_t sw = (uint32_t)lane & 7u;
     bool ok = true;
+    uint32_t mbits = 0u;                                          // running max|D| (see track_amax)
     auto release_accumulator = [&]() {
       tc_fence_before();
       __syncwarp();
@@ -340,6 +341,7 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           uint32_t r[32];
           tc_ld_32x32b_x32(taddr + 32 * ch, r);
           tc_wait_ld();
+          if (p.d_amax_out != nullptr) track_amax(p, r, alpha, row0 + lane, col0 + 32 * ch, mbits);
 #pragma unroll
           for (int q = 0; q < 16; ++q) {
             __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[2 * q]) * alpha, __uint_as_float(r[2 * q + 1]) * alpha);
@@ -366,6 +368,7 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
           tc_ld_32x32b_x32(taddr + 32 * ch, r);
           tc_wait_ld();
           if (ch == chunks - 1) release_accumulator();
+          if (p.d_amax_out != nullptr) track_amax(p, r, alpha, row0 + lane, col0 + 32 * ch, mbits);
           if (!p.tma_store) {
             if (row0 + lane < p.M) store_row_chunk(p, row0 + lane, col0 + 32 * ch, r, alpha);
             continue;
@@ -381,6 +384,7 @@ gemm3_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ 
       }
     }
     box_free();                                                   // before shared memory goes away
+    flush_amax(p, mbits, lane);
   }
   tc_fence_before();
   __syncthreads();

@@ -26,10 +26,12 @@ def gemm_status(device=None) -> int:
     return int(_status_word(device).item())
 
 
-def nvfp4_mm(a: NVFP4Tensor, b: NVFP4Tensor, out_dtype=None, out=None) -> torch.Tensor:
+def nvfp4_mm(a: NVFP4Tensor, b: NVFP4Tensor, out_dtype=None, out=None, amax_out=None) -> torch.Tensor:
     """a @ b for a = quant(A) [M, K] and b = quant(B.t()).t() (a transposed view whose storage is
     [N, K]): the call shape of torchao's _addmm_nvfp4_dispatch(a, b, aten.mm) at nvfp4_gemm.py:57.
-    fp32 accumulation; result in out_dtype (default: a's original dtype, bf16 unless fp32)."""
+    fp32 accumulation; result in out_dtype (default: a's original dtype, bf16 unless fp32).
+    amax_out: optional 1-element fp32 CUDA tensor that the GEMM epilogue fills with max|result|, so
+    that quant_nvfp4(result, amax=amax_out) needs no pass of its own to find it."""
     if a._transposed or not b._transposed:
         raise ValueError("nvfp4_mm expects a = quant(A) and b = quant(B.t()).t()")
     m, k2 = a.qdata.shape
@@ -44,14 +46,19 @@ def nvfp4_mm(a: NVFP4Tensor, b: NVFP4Tensor, out_dtype=None, out=None) -> torch.
         out_dtype = torch.float32 if a.orig_dtype == torch.float32 else torch.bfloat16
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise ValueError("out_dtype must be bfloat16 or float32")
-    dev = _lib.cuda_device_of(a.qdata, a.scale, a.per_tensor_scale, b.qdata, b.scale, b.per_tensor_scale, out)
+    if amax_out is not None and (amax_out.dtype != torch.float32 or amax_out.numel() != 1):
+        raise ValueError("amax_out must be a 1-element float32 tensor")
+    dev = _lib.cuda_device_of(a.qdata, a.scale, a.per_tensor_scale, b.qdata, b.scale, b.per_tensor_scale, out, amax_out)
     d = out if out is not None else torch.empty((m, n), dtype=out_dtype, device=dev)
-    with torch.cuda.device(dev):                   # the C side launches on the current device
-        code = _lib.lib().nvfp4_gemm(
-            a.qdata.data_ptr(), a.scale.data_ptr(), a.per_tensor_scale.data_ptr(),
+    args = (a.qdata.data_ptr(), a.scale.data_ptr(), a.per_tensor_scale.data_ptr(),
             b.qdata.data_ptr(), b.scale.data_ptr(), b.per_tensor_scale.data_ptr(),
             d.data_ptr(), _lib.OUT_F32 if out_dtype == torch.float32 else _lib.OUT_BF16,
-            m, n, k2 * 2, d.stride(0), _status_word(dev).data_ptr(), _stream(dev))
+            m, n, k2 * 2, d.stride(0))
+    with torch.cuda.device(dev):                   # the C side launches on the current device
+        if amax_out is None:
+            code = _lib.lib().nvfp4_gemm(*args, _status_word(dev).data_ptr(), _stream(dev))
+        else:
+            code = _lib.lib().nvfp4_gemm_amax(*args, amax_out.data_ptr(), _status_word(dev).data_ptr(), _stream(dev))
     _lib.check(code, "nvfp4_gemm")
     return d
 

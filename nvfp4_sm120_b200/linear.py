@@ -103,7 +103,7 @@ class FP4LinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, H, signs, wq_K, wq_N, amax_reduce=None, sharded=(False, False), x_amax=None,
-                x_amax_rht=True, dx_reduce=None):
+                x_amax_rht=True, dx_reduce=None, y_amax_out=None):
         # dx_reduce: optional callable(dx) -> handle with .wait(): starts the sum of the input gradient
         # over a tensor-parallel group right after the dgrad GEMM, so that it runs beside the wgrad
         # quantizations and GEMM; the handle is waited for before the backward returns
@@ -114,6 +114,8 @@ class FP4LinearFn(torch.autograd.Function):
         # passes over x would find); the token count must then be a multiple of 16
         if x_amax is not None and (x2.shape[0] % BLK != 0 or x2.dtype != torch.bfloat16):
             x_amax = None
+        if x_amax is not None and x_amax.numel() == 1:           # the plain maximum only
+            x_amax_rht = False
         x_red = amax_reduce if x_sharded else None
         if x_amax is not None and x_red is not None:
             # both maxima of a sharded x in ONE collective; the backward reuses the second
@@ -124,7 +126,9 @@ class FP4LinearFn(torch.autograd.Function):
         xq = _quant(x2, x_red, amax=None if x_amax is None else x_amax[0:1])
         if wq_K is None:
             wq_K = _quant(w, amax_reduce)
-        y = nvfp4_mm(xq, wq_K.t(), torch.bfloat16)
+        # y_amax_out: optional fp32 [1] that the fprop GEMM's epilogue fills with max|y| (for a consumer
+        # that quantizes y next; only meaningful when y stays bf16, i.e. x is bf16)
+        y = nvfp4_mm(xq, wq_K.t(), torch.bfloat16, amax_out=y_amax_out)
         ctx.save_for_backward(x2, w)
         ctx.H, ctx.signs, ctx.xshape, ctx.wq_N = H, signs, x.shape, wq_N
         ctx.amax_reduce, ctx.sharded, ctx.x_amax = amax_reduce, sharded, x_amax
@@ -173,7 +177,7 @@ class FP4LinearFn(torch.autograd.Function):
             dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
         if pending is not None:
             pending.wait()
-        return dx, dw, None, None, None, None, None, None, None, None, None
+        return dx, dw, None, None, None, None, None, None, None, None, None, None
 
 
 def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False, amax=None, counter=None):
@@ -241,15 +245,18 @@ class FP4Linear(nn.Module):
     def _wq_N(self):
         return self._cache.wq_N
 
-    def forward(self, x, amax=None, amax_signs=None):
-        """amax: optional fp32 [2] from a fused producer of x (see FP4LinearFn.forward); amax_signs: the
-        sign vector its Hadamard maximum was computed with (None = this layer's own).  When it is not
-        this layer's vector, only the plain maximum is used and the other is recomputed."""
+    def forward(self, x, amax=None, amax_signs=None, amax_out=None):
+        """amax: optional fp32 [2] from a fused producer of x (see FP4LinearFn.forward), or fp32 [1] = the
+        plain maximum alone; amax_signs: the sign vector its Hadamard maximum was computed with (None =
+        this layer's own).  When it is not this layer's vector, only the plain maximum is used and the
+        other is recomputed.  amax_out: optional fp32 [1] CUDA tensor the forward GEMM fills with max|y|
+        (bf16 activations), to be handed to the next layer as its `amax`."""
         if x.is_cuda and torch.is_autocast_enabled("cuda"):
             x = x.to(torch.get_autocast_dtype("cuda"))       # what autocast does for nn.Linear
         wq_K, wq_N = self._cache.get(self.weight)
         rht_ok = amax_signs is None or _same_signs(amax_signs, self.signs)
-        return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, None, (False, False), amax, rht_ok)
+        return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, None, (False, False), amax, rht_ok,
+                                 None, amax_out)
 
     def extra_repr(self):
         return f"in_features={self.weight.shape[1]}, out_features={self.weight.shape[0]}, bias=False, nvfp4"

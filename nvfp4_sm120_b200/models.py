@@ -14,6 +14,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from .linear import FP4Linear, make_linear
+from .norm import rmsnorm_amax
 from .swiglu import relu2
 
 
@@ -71,19 +72,36 @@ class DecoderBlock(nn.Module):
         # `down`'s sign vector; a consumer holding another vector recomputes its maximum (checked at
         # call time: a checkpoint may change the buffers)
         self.fused_act = bool(use_fp4) and isinstance(self.up, FP4Linear) and isinstance(self.down, FP4Linear)
+        # the norms in front of FP4 projections run as the fused kernel that also finds the maxima of
+        # its output (one sign vector serves q, k, v; each consumer checks it against its own)
+        self.fused_norm = bool(use_fp4) and all(isinstance(m, FP4Linear) for m in (self.q, self.k, self.v, self.up))
+
+    def _norm(self, norm, x, consumer):
+        """norm(x) -> (h, maxima or None): the fused kernel when the consumers are FP4Linear on the GPU."""
+        if (self.fused_norm and x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.shape[-1] % 8 == 0
+                and norm.weight is not None and norm.weight.dtype == torch.float32):
+            tokens = x.numel() // x.shape[-1]
+            return rmsnorm_amax(x, norm.weight, norm.eps, consumer.signs if tokens % 16 == 0 else None)
+        return norm(x), None
 
     def forward(self, x, cos, sin):
         B, T, _ = x.shape
-        h = self.norm_attn(x)
+        h, h_max = self._norm(self.norm_attn, x, self.q)
         split = lambda t, n: t.view(B, T, n, self.head_dim).transpose(1, 2)
-        q, k, v = split(self.q(h), self.n_heads), split(self.k(h), self.n_kv), split(self.v(h), self.n_kv)
+        if h_max is not None:
+            kw = dict(amax=h_max, amax_signs=self.q.signs)
+            q, k, v = self.q(h, **kw), self.k(h, **kw), self.v(h, **kw)
+        else:
+            q, k, v = self.q(h), self.k(h), self.v(h)
+        q, k, v = split(q, self.n_heads), split(k, self.n_kv), split(v, self.n_kv)
         q, k = apply_rotary(q, cos, sin), apply_rotary(k, cos, sin)
         if self.n_kv != self.n_heads:
             rep = self.n_heads // self.n_kv
             k, v = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
         att = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         x = x + self.o(att.transpose(1, 2).reshape(B, T, -1))
-        u = self.up(self.norm_mlp(x))
+        h2, h2_max = self._norm(self.norm_mlp, x, self.up)
+        u = self.up(h2, amax=h2_max, amax_signs=self.up.signs) if h2_max is not None else self.up(h2)
         if (self.fused_act and isinstance(self.down, FP4Linear) and u.is_cuda and u.dtype == torch.bfloat16
                 and u.shape[-1] % 8 == 0):
             # fused relu^2 that also hands `down` the maxima of its input (and `up` those of its gradient)

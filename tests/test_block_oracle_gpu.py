@@ -73,7 +73,11 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / b.float().norm()).item()
 
 
-def test_decoder_block_forward_backward_match_oracle_recipe():
+@pytest.mark.parametrize("fused_norm,tol", [(False, TOL), (True, 5 * TOL)])
+def test_decoder_block_forward_backward_match_oracle_recipe(fused_norm, tol):
+    """fused_norm: the block's RMSNorms run as the fused kernel that hands the projections their maxima.
+    Its output h is bf16, so the three gradients that meet at h (from q, k, v) are summed in bf16 where
+    the torch norm of the oracle run sums them in fp32: a wider, still small, bound."""
     import nvfp4_sm120_b200 as Q
     from nvfp4_sm120_b200 import quant
     from nvfp4_sm120_b200.models import DecoderBlock, rotary_tables
@@ -82,7 +86,8 @@ def test_decoder_block_forward_backward_match_oracle_recipe():
     dim, heads, hidden, B, T = 128, 4, 512, 2, 64
     torch.manual_seed(5)
     blk = DecoderBlock(dim, heads, heads, hidden, True, "cuda")
-    assert blk.fused_act
+    assert blk.fused_act and blk.fused_norm
+    blk.fused_norm = fused_norm
     shared = {"seeds": [4000], "order": [], "made": []}
     ref = DecoderBlock(dim, heads, heads, hidden, True, "cuda",
                        linear_factory=lambda cin, cout: _OracleLinear(cin, cout, shared))
@@ -127,6 +132,6 @@ def test_decoder_block_forward_backward_match_oracle_recipe():
     print("relative distance (to the oracle recipe, to the bf16 block):",
           {k: (float(f"{a:.2e}"), round(b, 4)) for k, (a, b) in report.items()})
     for k, (to_ref, to_bf16) in report.items():
-        assert to_ref < TOL, (k, to_ref)
+        assert to_ref < tol, (k, to_ref)
         assert to_ref < 0.1 * to_bf16, (k, to_ref, to_bf16)
     assert Q.gemm_status() == 0

@@ -225,3 +225,36 @@ def test_fp4_output_epilogue_equals_quantizing_the_bf16_output(Q, mnk, mode):
         z = Q.nvfp4_mm(got, w2.t(), out_dtype=torch.float32)
         z_ref = Q.nvfp4_mm(Q.quant_nvfp4(y, amax=amax), w2.t(), out_dtype=torch.float32)
         assert torch.equal(z, z_ref)
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("shape,dtype", [((512, 768, 512), torch.bfloat16), ((300, 200, 256), torch.bfloat16),
+                                         ((130, 1000, 128), torch.float32), ((128, 264, 2048), torch.float32),
+                                         ((100, 90, 64), torch.bfloat16)])
+def test_epilogue_amax_equals_a_pass_over_the_output(Q, mode, shape, dtype):
+    """nvfp4_gemm_amax: the word the epilogue leaves is max|D| of the stored output, bit for bit what a
+    reduction over D finds (whole tiles, clipped tiles, a row pitch that rules the TMA store out, both
+    output types and both kernels), and quantizing D with it equals the two-pass quantization."""
+    from nvfp4_sm120_b200 import _lib
+    from nvfp4_sm120_b200.gemm import nvfp4_mm
+    m, n, k = shape
+    qa = Q.quant_nvfp4(O.synthetic_tensor(m, k, 61).cuda())
+    qb = Q.quant_nvfp4(O.synthetic_tensor(n, k, 62).cuda())
+    word = torch.full((1,), 123.0, dtype=torch.float32, device="cuda")   # the call zeroes it first
+    try:
+        _lib.lib().nvfp4_gemm_set_mode(mode)
+        d = nvfp4_mm(qa, qb.t(), dtype, amax_out=word)
+        plain = nvfp4_mm(qa, qb.t(), dtype)
+    finally:
+        _lib.lib().nvfp4_gemm_set_mode(0)
+    if dtype == torch.float32 and k >= 2048 and mode != 2:
+        # the plain call splits K over CTAs here (partial sums added by atomics); this one does not
+        assert ((d - plain).norm() / plain.norm()).item() < 1e-5
+    else:
+        assert torch.equal(d, plain)
+    assert float(word) == float(d.abs().max().float()) and float(word) > 0
+    if dtype == torch.bfloat16 and n % 16 == 0:
+        q1, q2 = Q.quant_nvfp4(d, amax=word), Q.quant_nvfp4(d)
+        assert torch.equal(q1.qdata, q2.qdata) and torch.equal(q1.scale.view(torch.uint8), q2.scale.view(torch.uint8))
+        assert torch.equal(q1.per_tensor_scale, q2.per_tensor_scale)
+    assert Q.gemm_status() == 0

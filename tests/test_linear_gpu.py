@@ -135,3 +135,31 @@ def test_make_linear(Q):
     assert isinstance(lin, torch.nn.Linear) and lin.bias is None
     with pytest.raises(AssertionError):
         Q.FP4Linear(40, 32)
+
+
+def test_chained_linears_pass_the_maximum_through_the_gemm_epilogue(Q):
+    """y = l1(x, amax_out=word); z = l2(y, amax=word): the first layer's GEMM leaves max|y| for the second
+    layer's quantizer.  Outputs and all gradients equal those of the plain chain, bit for bit."""
+    from nvfp4_sm120_b200 import quant
+    torch.manual_seed(11)
+    l1, l2 = Q.FP4Linear(256, 512), Q.FP4Linear(512, 128)
+    x0 = torch.randn(192, 256, device="cuda", dtype=torch.bfloat16)
+    gz = torch.randn(192, 128, device="cuda", dtype=torch.bfloat16)
+
+    def run(chained):
+        for l in (l1, l2):
+            l.weight.grad = None
+        quant._SEED[0] = 500
+        x = x0.clone().requires_grad_(True)
+        if chained:
+            word = torch.zeros(1, dtype=torch.float32, device="cuda")
+            y = l1(x, amax_out=word)
+            assert float(word) == float(y.detach().abs().max().float())
+            z = l2(y, amax=word)
+        else:
+            z = l2(l1(x))
+        z.backward(gz)
+        return z.detach(), x.grad, l1.weight.grad.clone(), l2.weight.grad.clone()
+
+    for a, b in zip(run(True), run(False)):
+        assert torch.equal(a, b)
