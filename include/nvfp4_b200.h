@@ -145,6 +145,36 @@ int nvfp4_quantize_weight_bf16(const void* w, int64_t rows, int64_t cols, int64_
                                uint8_t* qdata_cols, uint8_t* scales_cols, float* pts_out, void* stream);
 
 /*
+ * Both quantized layouts of an ACTIVATION or GRADIENT x[rows, cols] (bf16, row stride ld) from ONE
+ * read, each with its own rounding mode, per-tensor maximum, seed and Philox counters:
+ *   qdata_rows / scales_rows / pts_rows   x itself, blocks along cols, no Hadamard: the bytes of
+ *       nvfp4_quantize_shard_bf16(transpose 0, mode_rows, rht 0, amax_rows, seed_rows)
+ *   qdata_cols / scales_cols / pts_cols   x^T [cols, rows], blocks along the rows of x, random-sign
+ *       Hadamard along those rows: the bytes of nvfp4_quantize_shard_bf16(transpose 1, mode_cols,
+ *       rht 1, amax_cols, seed_cols)
+ * amax_cols is the maximum AFTER the Hadamard transform (nvfp4_amax_both_bf16 gives both maxima
+ * from one read; a fused producer may know them already).  counters4 = {pitch_rows, base_rows,
+ * pitch_cols, base_cols} as in nvfp4_quantize_shard_bf16, or NULL for a whole tensor.
+ * Requirements: rows % 16 == 0, cols % 16 == 0, 16-byte aligned pointers, ld % 8 == 0.
+ * Replaces the pairs quant(x) / quant(x.t(), rht) and quant(gy, SR) / quant(gy.t(), rht, SR) of
+ * FP4LinearFn (nvfp4_train.py:36-38, 44-55), which read the tensor once per layout (and once more
+ * per maximum).
+ */
+int nvfp4_quantize_dual_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode_rows, int mode_cols,
+                             const float* signs16, const float* amax_rows, const float* amax_cols,
+                             uint64_t seed_rows, uint64_t seed_cols, uint64_t offset, const uint64_t* counters4,
+                             uint8_t* qdata_rows, uint8_t* scales_rows, float* pts_rows,
+                             uint8_t* qdata_cols, uint8_t* scales_cols, float* pts_cols, void* stream);
+
+/*
+ * maxima2[0] = max|x| and maxima2[1] = max|RHT_rows(x)| (16-point random-sign Hadamard over groups
+ * of 16 rows) from one read of x[rows, cols]; rows % 16 == 0, cols even.  The two words are what
+ * nvfp4_amax_bf16 gives with (rht 0) and with (rht 1, transpose 1).
+ */
+int nvfp4_amax_both_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, const float* signs16,
+                         float* maxima2, int zero_first, void* stream);
+
+/*
  * nvfp4_quantize_fused_bf16 for callers that cannot allocate device memory where they call from
  * (a C / FFI binding inside a runtime that gave all of HBM to its own pool, a callback that must
  * not hit cudaMalloc's implicit synchronisation): the kernel's scratch is a 256-byte device array

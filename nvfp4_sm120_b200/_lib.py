@@ -51,6 +51,12 @@ _SIGS = {
                                      _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
     "nvfp4_rmsnorm_bwd": (_c.c_int, [_c.c_void_p, _c.c_int, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int,
                                      _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p]),
+    "nvfp4_quantize_dual_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
+                                            _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_uint64, _c.c_uint64,
+                                            _c.c_uint64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+                                            _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    "nvfp4_amax_both_bf16": (_c.c_int, [_c.c_void_p, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p,
+                                        _c.c_int, _c.c_void_p]),
     "nvfp4_gemm_set_mode": (_c.c_int, [_c.c_int]),
     "nvfp4_gemm_fp4out": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
                                      _c.c_int64, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p,

@@ -370,6 +370,119 @@ __global__ void __launch_bounds__(256) quant_weight_dual_kernel(const uint16_t* 
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// activations and gradients: both layouts from one read.  Every operand of FP4Linear is needed
+// twice: x row-wise for fprop and x^T (Hadamard along the tokens) for wgrad, dY row-wise
+// (stochastic) for dgrad and dY^T (Hadamard + stochastic) for wgrad (nvfp4_train.py:36-55).  Same
+// 64 x 64 tiling as the weight kernel above: thread (row t / 4, segment t % 4) encodes row-wise
+// block (row, segment) with the plain maximum, then thread (column t % 64, row block t / 64) reads
+// its 16 rows of one column from the shared tile, applies the random-sign Hadamard along the rows
+// and encodes the column-wise block with the maximum of the transformed tensor.  Each layout has
+// its own per-tensor maximum, seed and Philox counter (counter of a block = its index in the whole
+// tensor of that layout: out_row * pitch + base + k_block), so the bytes are those of the two
+// separate quantizations.
+// ---------------------------------------------------------------------------------------
+struct DualCounters { uint64_t pitch_r, base_r, pitch_c, base_c; };
+
+template <bool SR_R, bool SR_C>
+__global__ void __launch_bounds__(256) quant_act_dual_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
+                                                             int64_t ld, const float* __restrict__ signs16,
+                                                             const float* __restrict__ amax_r,
+                                                             const float* __restrict__ amax_c, uint64_t seed_r,
+                                                             uint64_t seed_c, uint64_t offset, DualCounters ctr,
+                                                             uint8_t* __restrict__ q_rows, uint8_t* __restrict__ sf_rows,
+                                                             float* __restrict__ pts_r, uint8_t* __restrict__ q_cols,
+                                                             uint8_t* __restrict__ sf_cols, float* __restrict__ pts_c) {
+  __shared__ uint16_t tile[64][66];          // 33 words per row: a column walk touches 16 different banks
+  const GlobalScale g_r = global_scale(amax_r), g_c = global_scale(amax_c);
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+    if (pts_r != nullptr) *pts_r = g_r.pts;
+    if (pts_c != nullptr) *pts_c = g_c.pts;
+  }
+  const int t = threadIdx.x;
+  const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
+  const int r = t >> 2, seg = t & 3;
+  const int64_t gr = r0 + r, gc = c0 + seg * 16;
+  const bool have = gr < rows && gc < cols;          // rows and cols are multiples of 16: a block is whole or absent
+  uint32_t wv[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+  if (have) {
+    const uint4* p = reinterpret_cast<const uint4*>(x + gr * ld + gc);
+    const uint4 a = __ldg(p), b = __ldg(p + 1);
+    wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w; wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) *reinterpret_cast<uint32_t*>(&tile[r][seg * 16 + 2 * j]) = wv[j];
+  if (have) {
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      v[2 * j] = bf16_lo(wv[j]);
+      v[2 * j + 1] = bf16_hi(wv[j]);
+    }
+    uint32_t lo, hi, sf;
+    const int64_t kb = gc >> 4;
+    encode_block<SR_R>(v, g_r, (uint64_t)gr * ctr.pitch_r + ctr.base_r + (uint64_t)kb, seed_r, offset, lo, hi, sf);
+    *reinterpret_cast<uint2*>(q_rows + gr * (cols >> 1) + kb * 8) = make_uint2(lo, hi);
+    sf_rows[sf_offset(gr, kb, ((cols >> 4) + 3) >> 2)] = (uint8_t)sf;
+  }
+  __syncthreads();
+  const int c = t & 63, rb = t >> 6;
+  const int64_t oc = c0 + c, orow0 = r0 + rb * 16;
+  if (oc < cols && orow0 < rows) {
+    float sg[16];
+    load_signs(signs16, sg);
+    float u[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) u[i] = __uint_as_float((uint32_t)tile[rb * 16 + i][c] << 16) * sg[i];
+    hadamard16_inplace(u);
+    uint32_t lo, hi, sf;
+    const int64_t kb = orow0 >> 4;
+    encode_block<SR_C>(u, g_c, (uint64_t)oc * ctr.pitch_c + ctr.base_c + (uint64_t)kb, seed_c, offset, lo, hi, sf);
+    *reinterpret_cast<uint2*>(q_cols + oc * (rows >> 1) + kb * 8) = make_uint2(lo, hi);
+    sf_cols[sf_offset(oc, kb, ((rows >> 4) + 3) >> 2)] = (uint8_t)sf;
+  }
+}
+
+// plain maximum and maximum after the Hadamard transform along the rows, from one read
+__global__ void __launch_bounds__(256) amax_both_cols_kernel(const uint16_t* __restrict__ x, int64_t rows,
+                                                             int64_t cols, int64_t ld,
+                                                             const float* __restrict__ signs16,
+                                                             float* __restrict__ maxima2) {
+  float sg[16];
+  load_signs(signs16, sg);
+  const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  const int64_t r_base = (int64_t)blockIdx.y * 64;
+  float m = 0.0f;
+  uint32_t mp = 0u;
+  if (c < cols) {
+#pragma unroll 1
+    for (int j = 0; j < 4; ++j) {
+      const int64_t r0 = r_base + 16 * j;
+      if (r0 >= rows) break;
+      const uint32_t* p = reinterpret_cast<const uint32_t*>(x + r0 * ld + c);
+      float v0[16], v1[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t w = __ldg(p + (size_t)i * (size_t)(ld >> 1));
+        mp = max(mp, max(w & 0x7fffu, (w >> 16) & 0x7fffu));
+        v0[i] = bf16_lo(w) * sg[i];
+        v1[i] = bf16_hi(w) * sg[i];
+      }
+      hadamard16_inplace(v0);
+      hadamard16_inplace(v1);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m = fmaxf(m, fmaxf(fabsf(v0[i]), fabsf(v1[i])));
+    }
+  }
+  m = warp_max(m);
+  const float fp = warp_max(__uint_as_float(mp << 16));
+  if ((threadIdx.x & 31) == 0) {
+    atomic_max_nonneg(maxima2, fp);
+    atomic_max_nonneg(maxima2 + 1, m);
+  }
+}
+
 static inline int grid_for(int64_t work_items, int threads, int max_blocks) {
   int64_t b = (work_items + threads - 1) / threads;
   if (b > max_blocks) b = max_blocks;
@@ -496,6 +609,62 @@ extern "C" int nvfp4_quantize_weight_bf16(const void* w, int64_t rows, int64_t c
   else
     quant_weight_dual_kernel<false><<<grid, 256, 0, stream>>>(wp, rows, cols, ld, amax, qdata_rows, scales_rows, qdata_cols,
                                                               scales_cols, pts_out);
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+
+
+extern "C" int nvfp4_amax_both_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, const float* signs16,
+                                    float* maxima2, int zero_first, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!x || !signs16 || !maxima2) return NVFP4_E_NULL;
+  if (rows <= 0 || cols <= 0 || ld < cols || (rows & 15) != 0 || (cols & 1) != 0) return NVFP4_E_SHAPE;
+  if (!aligned16(x) || (ld & 7) != 0 || !aligned16(signs16)) return NVFP4_E_ALIGN;
+  if (zero_first && cudaMemsetAsync(maxima2, 0, 2 * sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
+  dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
+  if (grid.y > 65535u) return NVFP4_E_LIMIT;
+  amax_both_cols_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), rows, cols, ld, signs16, maxima2);
+  return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
+}
+
+extern "C" int nvfp4_quantize_dual_bf16(const void* x, int64_t rows, int64_t cols, int64_t ld, int mode_rows,
+                                        int mode_cols, const float* signs16, const float* amax_rows,
+                                        const float* amax_cols, uint64_t seed_rows, uint64_t seed_cols, uint64_t offset,
+                                        const uint64_t* counters4, uint8_t* qdata_rows, uint8_t* scales_rows,
+                                        float* pts_rows, uint8_t* qdata_cols, uint8_t* scales_cols, float* pts_cols,
+                                        void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (!x || !signs16 || !amax_rows || !amax_cols || !qdata_rows || !scales_rows || !qdata_cols || !scales_cols)
+    return NVFP4_E_NULL;
+  if (rows <= 0 || cols <= 0 || ld < cols || (rows & 15) != 0 || (cols & 15) != 0) return NVFP4_E_SHAPE;
+  auto bad_mode = [](int m) { return m != NVFP4_ROUND_NEAREST && m != NVFP4_ROUND_STOCHASTIC; };
+  if (bad_mode(mode_rows) || bad_mode(mode_cols)) return NVFP4_E_MODE;
+  if (!aligned16(x) || (ld & 7) != 0 || !aligned16(qdata_rows) || !aligned16(qdata_cols) || !aligned16(scales_rows) ||
+      !aligned16(scales_cols) || !aligned16(signs16))
+    return NVFP4_E_ALIGN;
+  DualCounters ctr{(uint64_t)(cols >> 4), 0, (uint64_t)(rows >> 4), 0};      // the tensor is whole
+  if (counters4 != nullptr) ctr = DualCounters{counters4[0], counters4[1], counters4[2], counters4[3]};
+  // the hardware draws from a 32-bit counter word pair; keep both layouts' counters inside 2^64 trivially,
+  // and inside the documented 2^32 blocks per tensor
+  if ((uint64_t)rows * ctr.pitch_r + ctr.base_r >= (1ull << 32) || (uint64_t)cols * ctr.pitch_c + ctr.base_c >= (1ull << 32))
+    return NVFP4_E_LIMIT;
+  auto clear_if_padded = [&](uint8_t* sf, int64_t m, int64_t k) {
+    const int64_t sm = (m + 127) / 128 * 128, sk = (k / 16 + 3) / 4 * 4;
+    if (sm == m && sk == k / 16) return true;
+    return cudaMemsetAsync(sf, 0, (size_t)(sm * sk), stream) == cudaSuccess;
+  };
+  if (!clear_if_padded(scales_rows, rows, cols) || !clear_if_padded(scales_cols, cols, rows)) return NVFP4_E_LAUNCH;
+  const dim3 grid((unsigned)((cols + 63) / 64), (unsigned)((rows + 63) / 64));
+  if (grid.y > 65535u) return NVFP4_E_LIMIT;
+  const uint16_t* xp = static_cast<const uint16_t*>(x);
+  const bool sr_r = mode_rows == NVFP4_ROUND_STOCHASTIC, sr_c = mode_cols == NVFP4_ROUND_STOCHASTIC;
+#define NVFP4_LAUNCH_DUAL(R_, C_) \
+  quant_act_dual_kernel<R_, C_><<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax_rows, amax_cols, seed_rows, \
+      seed_cols, offset, ctr, qdata_rows, scales_rows, pts_rows, qdata_cols, scales_cols, pts_cols)
+  if (sr_r && sr_c) NVFP4_LAUNCH_DUAL(true, true);
+  else if (sr_r) NVFP4_LAUNCH_DUAL(true, false);
+  else if (sr_c) NVFP4_LAUNCH_DUAL(false, true);
+  else NVFP4_LAUNCH_DUAL(false, false);
+#undef NVFP4_LAUNCH_DUAL
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 

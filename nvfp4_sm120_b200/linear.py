@@ -20,8 +20,8 @@ import torch
 import torch.nn as nn
 
 from .gemm import nvfp4_mm
-from .quant import hadamard16, quant_nvfp4, quant_weight_nvfp4, tensor_amax
-from .tensor import BLK
+from .quant import hadamard16, quant_dual_nvfp4, quant_nvfp4, quant_weight_nvfp4, tensor_amax, tensor_amax_both
+from .tensor import BLK, NVFP4Tensor
 
 _STEP = [0]          # bumped once per optimizer step; the weight-quant cache keys on it
 # The reference also wants NVFP4_CUDA=1 before it amortizes, because only its CUDA backend can;
@@ -86,6 +86,20 @@ def _take_grad_amax(gy2, signs=None):
     return e[1][0:1], (e[1][1:2] if rht_ok else None)
 
 
+_DUAL = [True]
+# The one-read kernel wins where launches and re-reads dominate (measured on a B200: 43 us against 64 us
+# for the two layouts of a 4096 x 4096 tensor) and loses to the two streaming kernels on large tensors
+# (150 us against 127 us at 4096 x 28672), so it takes tensors up to this many elements.
+_DUAL_MAX_ELEMS = 1 << 24
+
+
+def set_dual_quant(flag: bool):
+    """Quantize every activation and gradient in both layouts from one read (the default), or with one
+    kernel per layout (False: the two-step path, kept for comparison and for tensors whose token count
+    is not a multiple of 16)."""
+    _DUAL[0] = bool(flag)
+
+
 def set_amortize(flag: bool):
     """Switch the per-step weight-quant cache on or off after import (tests, benchmarks)."""
     global _AMORTIZE
@@ -123,13 +137,29 @@ class FP4LinearFn(torch.autograd.Function):
             x_red(x_amax)
             x_red = None
         ctx.x_reduced = x_amax is not None and x_sharded and amax_reduce is not None
-        xq = _quant(x2, x_red, amax=None if x_amax is None else x_amax[0:1])
+        # Both layouts of x from ONE read when the weight gradient will want x^T: the row-wise operand
+        # for the GEMM below and the Hadamard-transformed transpose for wgrad, which then needs neither
+        # x nor another pass in backward.  (A sharded x without producer maxima keeps the two-step path:
+        # its maxima are reduced over the group one by one.)
+        have_both = x_amax is not None and x_amax_rht and x_amax.numel() >= 2
+        dual = (_DUAL[0] and ctx.needs_input_grad[1] and x2.is_cuda and x2.shape[0] % BLK == 0
+                and x2.numel() <= _DUAL_MAX_ELEMS and (x_red is None) and (have_both or not x_sharded))
+        xtq = None
+        if dual:
+            xq, xtq = quant_dual_nvfp4(x2, signs, None if x_amax is None else x_amax[0:1],
+                                       x_amax[1:2] if have_both else None)
+        else:
+            xq = _quant(x2, x_red, amax=None if x_amax is None else x_amax[0:1])
         if wq_K is None:
             wq_K = _quant(w, amax_reduce)
         # y_amax_out: optional fp32 [1] that the fprop GEMM's epilogue fills with max|y| (for a consumer
         # that quantizes y next; only meaningful when y stays bf16, i.e. x is bf16)
         y = nvfp4_mm(xq, wq_K.t(), torch.bfloat16, amax_out=y_amax_out)
-        ctx.save_for_backward(x2, w)
+        if xtq is None:
+            ctx.save_for_backward(x2, w)
+        else:
+            ctx.save_for_backward(w, xtq.qdata, xtq.scale, xtq.per_tensor_scale)
+        ctx.have_xtq = xtq is not None
         ctx.H, ctx.signs, ctx.xshape, ctx.wq_N = H, signs, x.shape, wq_N
         ctx.amax_reduce, ctx.sharded, ctx.x_amax = amax_reduce, sharded, x_amax
         ctx.x_amax_rht = bool(x_amax_rht)        # False: the Hadamard maximum came from another sign vector
@@ -138,7 +168,13 @@ class FP4LinearFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gy):
-        x2, w = ctx.saved_tensors
+        if ctx.have_xtq:
+            w, xt_q, xt_s, xt_p = ctx.saved_tensors
+            x2 = None
+            xtq = NVFP4Tensor(xt_q, xt_s, BLK, torch.bfloat16, xt_p, True)
+        else:
+            x2, w = ctx.saved_tensors
+            xtq = None
         H, signs, wq_N, red = ctx.H, ctx.signs, ctx.wq_N, ctx.amax_reduce
         x_sharded, y_sharded = ctx.sharded[0], ctx.sharded[1]
         gy2 = gy.reshape(-1, w.shape[0])
@@ -152,7 +188,17 @@ class FP4LinearFn(torch.autograd.Function):
             ctr_cols = (tokens // BLK, rank * n_local * (tokens // BLK))
         g_amax, g_amax_rht = _take_grad_amax(gy2, signs)      # known to a fused producer of gy, else None
         g_red = red if y_sharded else None
-        if g_amax is not None and g_red is not None:
+        # dY in both layouts from one read when both gradients are wanted (a sharded dY needs its
+        # counters, which come with the rank)
+        dual_g = (_DUAL[0] and ctx.needs_input_grad[0] and ctx.needs_input_grad[1] and gy2.is_cuda
+                  and gy2.shape[0] % BLK == 0 and gy2.numel() <= _DUAL_MAX_ELEMS
+                  and (g_red is None or ctr_rows is not None))
+        if dual_g and (g_amax is None or g_amax_rht is None):
+            both = tensor_amax_both(gy2, signs)               # one read for the two maxima
+            if g_red is not None:
+                g_red(both)
+            g_amax, g_amax_rht = both[0:1], both[1:2]
+        elif g_amax is not None and g_red is not None:
             # a sharded gradient: reduce the producer's maxima over the group, both in ONE collective
             both = torch.cat([g_amax, g_amax_rht]) if g_amax_rht is not None else g_amax.clone()
             g_red(both)
@@ -162,18 +208,25 @@ class FP4LinearFn(torch.autograd.Function):
         # when it has to be recomputed here (none given, or another sign vector) it is reduced here
         xt_red = None if (x_amax_rht is not None and ctx.x_reduced) else (red if x_sharded else None)
         dx = dw = None
+        gq = gtq = None
+        if dual_g:
+            counters = None if ctr_rows is None else (ctr_rows[0], ctr_rows[1], ctr_cols[0], ctr_cols[1])
+            gq, gtq = quant_dual_nvfp4(gy2, signs, g_amax, g_amax_rht, True, True, counters=counters)
         if ctx.needs_input_grad[0]:
             # dgrad: dX = dY @ W, contraction over N; dY gets stochastic rounding
-            gq = _quant(gy2, None if g_amax is not None else g_red, stochastic=True, amax=g_amax, counter=ctr_rows)
+            if gq is None:
+                gq = _quant(gy2, None if g_amax is not None else g_red, stochastic=True, amax=g_amax, counter=ctr_rows)
             if wq_N is None:
                 wq_N = _quant(w, red, transpose=True)
             dx = nvfp4_mm(gq, wq_N.t(), torch.bfloat16).reshape(ctx.xshape).to(gy.dtype)
         pending = ctx.dx_reduce(dx) if (dx is not None and ctx.dx_reduce is not None) else None
         if ctx.needs_input_grad[1]:
             # wgrad: dW = dY^T @ X, contraction over tokens; Hadamard on both, SR on the gradient
-            gtq = _quant(gy2, None if g_amax_rht is not None else g_red, stochastic=True, rht=True, H=H, signs=signs,
-                         transpose=True, amax=g_amax_rht, counter=ctr_cols)
-            xtq = _quant(x2, xt_red, rht=True, H=H, signs=signs, transpose=True, amax=x_amax_rht)
+            if gtq is None:
+                gtq = _quant(gy2, None if g_amax_rht is not None else g_red, stochastic=True, rht=True, H=H, signs=signs,
+                             transpose=True, amax=g_amax_rht, counter=ctr_cols)
+            if xtq is None:
+                xtq = _quant(x2, xt_red, rht=True, H=H, signs=signs, transpose=True, amax=x_amax_rht)
             dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
         if pending is not None:
             pending.wait()

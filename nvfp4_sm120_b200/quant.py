@@ -185,5 +185,74 @@ def quant_weight_nvfp4(w, amax=None, two_d=False):
             NVFP4Tensor(q_c, s_c.view(torch.float8_e4m3fn), BLK, w.dtype, pts, True))
 
 
+def tensor_amax_both(t, signs):
+    """fp32 [2] = (max|t|, max|RHT_rows(t)|) from one read of t [rows, cols] (rows % 16 == 0): what
+    tensor_amax(t) and tensor_amax(t, True, signs, transpose=True) find in two."""
+    x = _as_bf16_rows(t)
+    sg = _signs(signs, x.device)
+    dev = _lib.cuda_device_of(x, sg)
+    maxima = torch.empty(2, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        code = _lib.lib().nvfp4_amax_both_bf16(x.data_ptr(), x.shape[0], x.shape[1], x.stride(0), sg.data_ptr(),
+                                               maxima.data_ptr(), 1, _stream(dev))
+    _lib.check(code, "nvfp4_amax_both_bf16")
+    return maxima
+
+
+def quant_dual_nvfp4(t, signs, amax_rows=None, amax_cols=None, stochastic_rows=False, stochastic_cols=False,
+                     seed_rows=None, seed_cols=None, philox_offset=0, counters=None):
+    """(quant_nvfp4(t, stochastic_rows), quant_nvfp4(t, stochastic_cols, rht=True, signs=signs,
+    transpose=True)) from ONE read of t [rows, cols]: the operand and its Hadamard-transformed
+    transpose, which FP4Linear needs of every activation and gradient (nvfp4_train.py:36-55).
+    amax_rows / amax_cols: 1-element fp32 CUDA tensors (the plain maximum and the maximum after the
+    Hadamard transform along the rows); both are found in one extra read when either is missing.
+    Seeds left None come from the module counter in the order rows, cols, as two separate stochastic
+    calls would draw them.  counters: (pitch_rows, base_rows, pitch_cols, base_cols) for a shard."""
+    if seed_rows is None:
+        seed_rows = _SEED[0]
+        if stochastic_rows:
+            _SEED[0] += 1
+    if seed_cols is None:
+        seed_cols = _SEED[0]
+        if stochastic_cols:
+            _SEED[0] += 1
+    x = _as_bf16_rows(t)
+    rows, cols = x.shape
+    if rows % BLK != 0 or cols % BLK != 0:
+        raise AssertionError(f"dims {rows}x{cols} must be divisible by {BLK}")
+    dev = x.device
+    sg = _signs(signs, dev)
+    if amax_rows is None and amax_cols is None:
+        both = tensor_amax_both(x, sg)
+        amax_rows, amax_cols = both[0:1], both[1:2]
+    elif amax_cols is None:
+        amax_cols = tensor_amax(x, True, sg, transpose=True)
+    elif amax_rows is None:
+        amax_rows = tensor_amax(x)
+    _lib.cuda_device_of(x, sg, amax_rows, amax_cols)
+    sm_r, sk_r = swizzled_scale_dims(rows, cols)
+    sm_c, sk_c = swizzled_scale_dims(cols, rows)
+    q_r = torch.empty((rows, cols // 2), dtype=torch.uint8, device=dev)
+    s_r = torch.empty((sm_r, sk_r), dtype=torch.uint8, device=dev)
+    q_c = torch.empty((cols, rows // 2), dtype=torch.uint8, device=dev)
+    s_c = torch.empty((sm_c, sk_c), dtype=torch.uint8, device=dev)
+    pts_r = torch.empty((), dtype=torch.float32, device=dev)
+    pts_c = torch.empty((), dtype=torch.float32, device=dev)
+    ctr = None
+    if counters is not None:
+        import ctypes
+        ctr = (ctypes.c_uint64 * 4)(*[int(v) for v in counters])
+    mode = lambda sr: _lib.ROUND_STOCHASTIC if sr else _lib.ROUND_NEAREST
+    with torch.cuda.device(dev):
+        code = _lib.lib().nvfp4_quantize_dual_bf16(
+            x.data_ptr(), rows, cols, x.stride(0), mode(stochastic_rows), mode(stochastic_cols), sg.data_ptr(),
+            amax_rows.data_ptr(), amax_cols.data_ptr(), int(seed_rows) & (2 ** 64 - 1), int(seed_cols) & (2 ** 64 - 1),
+            int(philox_offset), ctr, q_r.data_ptr(), s_r.data_ptr(), pts_r.data_ptr(), q_c.data_ptr(), s_c.data_ptr(),
+            pts_c.data_ptr(), _stream(dev))
+    _lib.check(code, "nvfp4_quantize_dual_bf16")
+    return (NVFP4Tensor(q_r, s_r.view(torch.float8_e4m3fn), BLK, t.dtype, pts_r, True),
+            NVFP4Tensor(q_c, s_c.view(torch.float8_e4m3fn), BLK, t.dtype, pts_c, True))
+
+
 # the reference's second name for the same entry (nvfp4_cuda.py:158)
 quant_nvfp4_cuda = quant_nvfp4
