@@ -698,6 +698,34 @@ def extras(Q, dev, bf16_peak, peak_kind):
     return out
 
 
+def gemm_case(which, m, n, k, launches=3):
+    """A few launches of one GEMM for a profiler: `ours` = nvfp4_mm, `library` = the cuBLASLt comparator
+    of the extras, both on the same quantized operands (config 3's generator)."""
+    import nvfp4_sm120_b200 as Q
+    from nvfp4_sm120_b200.gemm import nvfp4_mm
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(2)
+    qa = Q.quant_nvfp4(torch.randn(m, k, device=dev, dtype=torch.bfloat16, generator=g))
+    qb = Q.quant_nvfp4(torch.randn(n, k, device=dev, dtype=torch.bfloat16, generator=g))
+    if which == "library":
+        fn, note = library_fp4_mm(qa, qb)
+        if fn is None:
+            raise SystemExit("no library FP4 GEMM in this torch: " + note)
+    else:
+        out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+        fn, note = (lambda: nvfp4_mm(qa, qb.t(), out=out)), "nvfp4_mm"
+    fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) / launches * 1e3
+    print(f"{which} ({note}) {m}x{n}x{k}: {us:.1f} us per launch, {2.0 * m * n * k / us / 1e6:.0f} TFLOP/s")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -705,7 +733,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--gemm-case", choices=["ours", "library"], default=None,
+                    help="profiling aid: run a few launches of one FP4 GEMM (this build's kernel, or the library "
+                         "comparator on the same quantized operands), print the time and exit")
+    ap.add_argument("--mnk", type=int, nargs=3, default=[8192, 8192, 8192])
     args = ap.parse_args()
+    if args.gemm_case is not None:
+        gemm_case(args.gemm_case, *args.mnk)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
