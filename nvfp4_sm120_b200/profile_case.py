@@ -19,6 +19,9 @@ def main():
     ap.add_argument("--cols", type=int, default=8192)
     ap.add_argument("--mode", default="rne", choices=["rne", "sr", "rht_sr"])
     ap.add_argument("--transpose", action="store_true")
+    ap.add_argument("--rotate", type=int, default=1, help="quant: number of input tensors taken in turn (more than "
+                    "L2 / tensor size of them make every launch read HBM)")
+    ap.add_argument("--known-amax", action="store_true", help="quant: hand the quantizer the maximum (one-pass form)")
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -92,21 +95,26 @@ def main():
               f"{e0.elapsed_time(e1) / a.iters:.3f} ms per forward+backward")
         return
     if a.case == "quant":
-        x = torch.randn(a.rows, a.cols, device=dev, dtype=torch.bfloat16, generator=g)
+        xs = [torch.randn(a.rows, a.cols, device=dev, dtype=torch.bfloat16, generator=g) for _ in range(max(1, a.rotate))]
+        x = xs[0]
         signs = torch.ones(16, device=dev)
         kw = dict(stochastic=a.mode != "rne", rht=a.mode == "rht_sr", signs=signs, seed=7, transpose=a.transpose)
-        Q.quant_nvfp4(x, **kw)
+        if a.known_amax:                 # the same tensor values in every input: one maximum serves all
+            xs = [x] + [x.clone() for _ in xs[1:]]
+            kw["amax"] = Q.tensor_amax(x, kw["rht"], signs, a.transpose)
+        for xi in xs:
+            Q.quant_nvfp4(xi, **kw)
         torch.cuda.synchronize()
         e0.record()
-        for _ in range(a.iters):
-            Q.quant_nvfp4(x, **kw)
+        for i in range(a.iters):
+            Q.quant_nvfp4(xs[i % len(xs)], **kw)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / a.iters
         nbytes = a.rows * a.cols * (2 + 0.5 + 1 / 16)
         print(f"quant {a.rows}x{a.cols} {a.mode} transpose={a.transpose}: {ms * 1e3:.1f} us/iter, "
               f"{nbytes / ms / 1e6:.0f} GB/s algorithmic")
-        if not a.transpose:
+        if not a.transpose and not a.known_amax:
             from nvfp4_sm120_b200 import quant
             ws = quant._workspace(dev).cpu()         # start (u64 at byte 24), four u32 offsets, last end (u64)
             start, last_end = int(ws.view(torch.int64)[3]), int(ws.view(torch.int64)[6])
