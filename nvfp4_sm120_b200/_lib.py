@@ -5,7 +5,8 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libnvfp4_b200.so")
+# NVFP4_B200_LIB: another build of the same library (e.g. one compiled with different options)
+LIB_PATH = os.environ.get("NVFP4_B200_LIB") or os.path.join(_PKG, "libnvfp4_b200.so")
 
 OK = 0
 ROUND_NEAREST, ROUND_STOCHASTIC = 0, 1

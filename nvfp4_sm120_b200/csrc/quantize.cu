@@ -5,24 +5,44 @@
 // stream) -> packed nibbles, and writes the scale byte straight to its place in the 128x4-tiled
 // layout the tcgen05 block-scaled MMA reads.  The arithmetic follows the reference's pure-torch
 // quantizer operation by operation (nvfp4_gemm.py:36-45): true fp32 divisions, no fast-math.
-#include "common.cuh"
-#include "nvfp4_b200.h"
+#include "quantize_common.cuh"
 
 namespace nvfp4 {
 
+using fused::PhiloxKeys;
+
 // ---------------------------------------------------------------------------------------
-// shared per-block arithmetic
+// shared per-block arithmetic: that of the single-launch kernels (quantize_common.cuh) -- the block
+// scale byte by the checked one-multiply shortcut, (1 / pts) / scale from a 128-entry table made with
+// true divisions, Philox with host-made round keys -- so the bytes are the same and a block costs
+// about 80 instructions less than with three true divisions and in-kernel key updates.
 // ---------------------------------------------------------------------------------------
 struct GlobalScale {
-  float pts;       // amax / 2688
-  float inv_pts;   // 1 / pts
+  fused::Scale sc;          // pts = amax / 2688, 1 / pts, 1 / (6 pts)
+  const float* recip;       // shared memory: recip[b] = (1 / pts) / e4m3(b)
+  float pts;
 };
 
-__device__ __forceinline__ GlobalScale global_scale(const float* __restrict__ amax) {
+// Every thread of the CTA calls this (it holds a barrier); `tab` is 128 floats of shared memory.
+__device__ __forceinline__ GlobalScale global_scale(const float* __restrict__ amax, float* tab) {
   GlobalScale g;
-  g.pts = __fdiv_rn(fmaxf(__ldg(amax), kAmaxFloor), kGlobalDiv);
-  g.inv_pts = __fdiv_rn(1.0f, g.pts);
+  g.sc.pts = __fdiv_rn(fmaxf(__ldg(amax), kAmaxFloor), kGlobalDiv);
+  g.sc.inv_pts = __fdiv_rn(1.0f, g.sc.pts);
+  g.sc.c = __fdiv_rn(1.0f, kF4Max * g.sc.pts);
+  g.pts = g.sc.pts;
+  g.recip = tab;
+  if (threadIdx.x < 128) tab[threadIdx.x] = __fdiv_rn(g.sc.inv_pts, e4m3_to_f32(threadIdx.x));
+  __syncthreads();
   return g;
+}
+
+inline PhiloxKeys make_philox_keys(uint64_t seed) {
+  PhiloxKeys keys;
+  for (int r = 0; r < 10; ++r) {
+    keys.k[r][0] = (uint32_t)seed + (uint32_t)r * 0x9E3779B9u;
+    keys.k[r][1] = (uint32_t)(seed >> 32) + (uint32_t)r * 0xBB67AE85u;
+  }
+  return keys;
 }
 
 // v[16] (already Hadamard-transformed if wanted) -> 8 bytes of codes (lo, hi) and the E4M3 byte.
@@ -37,17 +57,14 @@ __device__ __forceinline__ float block_amax16(const float (&v)[16]) {
 // the 16 x 16 tile around it (2-D weight scaling, nvfp4_validate.py:68-82)
 template <bool SR>
 __device__ __forceinline__ void encode_block_scaled(const float (&v)[16], float amax, const GlobalScale& g,
-                                                    uint64_t blk_index, uint64_t seed, uint64_t offset,
+                                                    uint64_t blk_index, const PhiloxKeys& keys, uint64_t offset,
                                                     uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
-  const float bs = __fdiv_rn(amax, kF4Max);                                   // nvfp4_gemm.py:39
-  const float sbs = fminf(fmaxf(__fdiv_rn(bs, g.pts), kE4M3Eps), kE4M3Max);   // :40
-  sf_byte = f32_to_e4m3(sbs);
-  const float recip = __fdiv_rn(g.inv_pts, e4m3_to_f32(sf_byte));             // :41
+  sf_byte = fused::block_scale_byte(amax, g.sc);                   // nvfp4_gemm.py:39-40
+  const float recip = g.recip[sf_byte];                            // :41
   // the clamp to +-6 of :42 is the saturation of the conversions below
   if (SR) {
-    const Philox4 r = philox4x32_10((uint32_t)blk_index, (uint32_t)(blk_index >> 32),
-                                    (uint32_t)offset, (uint32_t)(offset >> 32),
-                                    (uint32_t)seed, (uint32_t)(seed >> 32));
+    const Philox4 r = fused::philox_rounds((uint32_t)blk_index, (uint32_t)(blk_index >> 32),
+                                           (uint32_t)offset, (uint32_t)(offset >> 32), keys);
     const uint32_t q0 = e2m1x4_rs(v[0] * recip, v[1] * recip, v[2] * recip, v[3] * recip, r.x);
     const uint32_t q1 = e2m1x4_rs(v[4] * recip, v[5] * recip, v[6] * recip, v[7] * recip, r.y);
     const uint32_t q2 = e2m1x4_rs(v[8] * recip, v[9] * recip, v[10] * recip, v[11] * recip, r.z);
@@ -55,18 +72,19 @@ __device__ __forceinline__ void encode_block_scaled(const float (&v)[16], float 
     lo = q0 | (q1 << 16);
     hi = q2 | (q3 << 16);
   } else {
-    lo = e2m1x2_rn(v[0] * recip, v[1] * recip) | (e2m1x2_rn(v[2] * recip, v[3] * recip) << 8) |
-         (e2m1x2_rn(v[4] * recip, v[5] * recip) << 16) | (e2m1x2_rn(v[6] * recip, v[7] * recip) << 24);
-    hi = e2m1x2_rn(v[8] * recip, v[9] * recip) | (e2m1x2_rn(v[10] * recip, v[11] * recip) << 8) |
-         (e2m1x2_rn(v[12] * recip, v[13] * recip) << 16) | (e2m1x2_rn(v[14] * recip, v[15] * recip) << 24);
+    float d[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) d[j] = v[j] * recip;
+    lo = fused::e2m1x8_rn(d);
+    hi = fused::e2m1x8_rn(d + 8);
   }
 }
 
 template <bool SR>
 __device__ __forceinline__ void encode_block(const float (&v)[16], const GlobalScale& g,
-                                             uint64_t blk_index, uint64_t seed, uint64_t offset,
+                                             uint64_t blk_index, const PhiloxKeys& keys, uint64_t offset,
                                              uint32_t& lo, uint32_t& hi, uint32_t& sf_byte) {
-  encode_block_scaled<SR>(v, block_amax16(v), g, blk_index, seed, offset, lo, hi, sf_byte);
+  encode_block_scaled<SR>(v, block_amax16(v), g, blk_index, keys, offset, lo, hi, sf_byte);
 }
 
 __device__ __forceinline__ void load_signs(const float* __restrict__ signs16, float (&sg)[16]) {
@@ -96,19 +114,26 @@ __global__ void __launch_bounds__(512) amax_plain_kernel(const uint16_t* __restr
                                                          int vec_per_row, int64_t ld,
                                                          float* __restrict__ amax) {
   const int64_t total = rows * vec_per_row;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   uint32_t m = 0;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
+  auto fold = [&](const uint4& q) {
+    const uint32_t k = 0x7fff7fffu;
+    const uint32_t a = __vimax3_u16x2(q.x & k, q.y & k, q.z & k);
+    m = __vimax3_u16x2(a, q.w & k, m);                 // both 16-bit halves of m carry a running maximum
+  };
+  auto load = [&](int64_t i) {
     const int64_t r = i / vec_per_row;
     const int cv = (int)(i - r * vec_per_row);
-    const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + r * ld) + cv);
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      m = max(m, w[j] & 0x7fffu);
-      m = max(m, (w[j] >> 16) & 0x7fffu);
-    }
+    return __ldg(reinterpret_cast<const uint4*>(x + r * ld) + cv);
+  };
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  // four 16-byte loads per thread in flight: one per thread leaves the memory system half idle
+  for (; i + 3 * stride < total; i += 4 * stride) {
+    const uint4 q0 = load(i), q1 = load(i + stride), q2 = load(i + 2 * stride), q3 = load(i + 3 * stride);
+    fold(q0); fold(q1); fold(q2); fold(q3);
   }
+  for (; i < total; i += stride) fold(load(i));
+  m = max(m & 0xffffu, m >> 16);
   float f = warp_max(__uint_as_float(m << 16));
   if ((threadIdx.x & 31) == 0) atomic_max_nonneg(amax, f);
 }
@@ -151,14 +176,15 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* __restr
                                                          int blk_per_row, int64_t ld,
                                                          const float* __restrict__ signs16,
                                                          const float* __restrict__ amax,
-                                                         uint64_t seed, uint64_t offset,
+                                                         const PhiloxKeys keys, uint64_t offset,
                                                          uint8_t* __restrict__ qdata,
                                                          uint8_t* __restrict__ scales,
                                                          float* __restrict__ pts_out,
                                                          uint64_t ctr_pitch, uint64_t ctr_base) {
   // Philox counter of block (row, kb) = row * ctr_pitch + ctr_base + kb: the block's index in the
   // whole tensor when x is a column shard of it (pitch = blocks per row of the whole tensor)
-  const GlobalScale g = global_scale(amax);
+  __shared__ float recip_tab[128];
+  const GlobalScale g = global_scale(amax, recip_tab);
   if (blockIdx.x == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
   float sg[16];
   if (RHT) load_signs(signs16, sg);
@@ -183,7 +209,7 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* __restr
       hadamard16_inplace(v);
     }
     uint32_t lo, hi, sf;
-    encode_block<SR>(v, g, (uint64_t)r * ctr_pitch + ctr_base + (uint64_t)kb, seed, offset, lo, hi, sf);
+    encode_block<SR>(v, g, (uint64_t)r * ctr_pitch + ctr_base + (uint64_t)kb, keys, offset, lo, hi, sf);
     *reinterpret_cast<uint2*>(qdata + i * 8) = make_uint2(lo, hi);
     scales[sf_offset(r, kb, col_tiles)] = (uint8_t)sf;
   }
@@ -241,13 +267,14 @@ __global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restr
                                                          int64_t cols, int64_t ld,
                                                          const float* __restrict__ signs16,
                                                          const float* __restrict__ amax,
-                                                         uint64_t seed, uint64_t offset,
+                                                         const PhiloxKeys keys, uint64_t offset,
                                                          uint8_t* __restrict__ qdata,
                                                          uint8_t* __restrict__ scales,
                                                          float* __restrict__ pts_out,
                                                          uint64_t ctr_pitch, uint64_t ctr_base) {
   // Philox counter of output block (column c, row block kb) = c * ctr_pitch + ctr_base + kb
-  const GlobalScale g = global_scale(amax);
+  __shared__ float recip_tab[128];
+  const GlobalScale g = global_scale(amax, recip_tab);
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
   float sg[16];
   if (RHT) load_signs(signs16, sg);
@@ -268,8 +295,8 @@ __global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restr
       load_col_pair_block<RHT>(x, ld, r0, c, sg, v0, v1);
       const uint64_t kb = (uint64_t)(r0 >> 4);
       uint32_t sf0, sf1;
-      encode_block<SR>(v0, g, (uint64_t)c * ctr_pitch + ctr_base + kb, seed, offset, q[0][2 * j], q[0][2 * j + 1], sf0);
-      encode_block<SR>(v1, g, (uint64_t)(c + 1) * ctr_pitch + ctr_base + kb, seed, offset, q[1][2 * j], q[1][2 * j + 1], sf1);
+      encode_block<SR>(v0, g, (uint64_t)c * ctr_pitch + ctr_base + kb, keys, offset, q[0][2 * j], q[0][2 * j + 1], sf0);
+      encode_block<SR>(v1, g, (uint64_t)(c + 1) * ctr_pitch + ctr_base + kb, keys, offset, q[1][2 * j], q[1][2 * j + 1], sf1);
       sfw[0] |= sf0 << (8 * j);
       sfw[1] |= sf1 << (8 * j);
       nvalid = j + 1;
@@ -313,7 +340,9 @@ __global__ void __launch_bounds__(256) quant_weight_dual_kernel(const uint16_t* 
   __shared__ uint16_t tile[64][66];          // 33 words per row: a column walk touches 16 different banks
   __shared__ float bmax[64][4];              // row-wise block maxima of the tile
   __shared__ float tmax[4][4];               // 16 x 16 tile maxima
-  const GlobalScale g = global_scale(amax);
+  __shared__ float recip_tab[128];
+  const GlobalScale g = global_scale(amax, recip_tab);
+  const PhiloxKeys keys{};                   // round to nearest: unused
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
   const int t = threadIdx.x;
   const int64_t r0 = (int64_t)blockIdx.y * 64, c0 = (int64_t)blockIdx.x * 64;
@@ -350,7 +379,7 @@ __global__ void __launch_bounds__(256) quant_weight_dual_kernel(const uint16_t* 
   // ---- row-wise output ----
   if (have) {
     uint32_t lo, hi, sf;
-    encode_block_scaled<false>(v, TWO_D ? tmax[r >> 4][seg] : my_max, g, 0, 0, 0, lo, hi, sf);
+    encode_block_scaled<false>(v, TWO_D ? tmax[r >> 4][seg] : my_max, g, 0, keys, 0, lo, hi, sf);
     const int64_t kb = gc >> 4;
     *reinterpret_cast<uint2*>(q_rows + gr * (cols >> 1) + kb * 8) = make_uint2(lo, hi);
     sf_rows[sf_offset(gr, kb, ((cols >> 4) + 3) >> 2)] = (uint8_t)sf;
@@ -363,7 +392,7 @@ __global__ void __launch_bounds__(256) quant_weight_dual_kernel(const uint16_t* 
 #pragma unroll
     for (int i = 0; i < 16; ++i) u[i] = __uint_as_float((uint32_t)tile[rb * 16 + i][c] << 16);
     uint32_t lo, hi, sf;
-    encode_block_scaled<false>(u, TWO_D ? tmax[rb][c >> 4] : block_amax16(u), g, 0, 0, 0, lo, hi, sf);
+    encode_block_scaled<false>(u, TWO_D ? tmax[rb][c >> 4] : block_amax16(u), g, 0, keys, 0, lo, hi, sf);
     const int64_t kb = orow0 >> 4;
     *reinterpret_cast<uint2*>(q_cols + oc * (rows >> 1) + kb * 8) = make_uint2(lo, hi);
     sf_cols[sf_offset(oc, kb, ((rows >> 4) + 3) >> 2)] = (uint8_t)sf;
@@ -389,13 +418,14 @@ template <bool SR_R, bool SR_C>
 __global__ void __launch_bounds__(256) quant_act_dual_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
                                                              int64_t ld, const float* __restrict__ signs16,
                                                              const float* __restrict__ amax_r,
-                                                             const float* __restrict__ amax_c, uint64_t seed_r,
-                                                             uint64_t seed_c, uint64_t offset, DualCounters ctr,
+                                                             const float* __restrict__ amax_c, const PhiloxKeys keys_r,
+                                                             const PhiloxKeys keys_c, uint64_t offset, DualCounters ctr,
                                                              uint8_t* __restrict__ q_rows, uint8_t* __restrict__ sf_rows,
                                                              float* __restrict__ pts_r, uint8_t* __restrict__ q_cols,
                                                              uint8_t* __restrict__ sf_cols, float* __restrict__ pts_c) {
   __shared__ uint16_t tile[64][66];          // 33 words per row: a column walk touches 16 different banks
-  const GlobalScale g_r = global_scale(amax_r), g_c = global_scale(amax_c);
+  __shared__ float recip_r[128], recip_c[128];
+  const GlobalScale g_r = global_scale(amax_r, recip_r), g_c = global_scale(amax_c, recip_c);
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
     if (pts_r != nullptr) *pts_r = g_r.pts;
     if (pts_c != nullptr) *pts_c = g_c.pts;
@@ -422,7 +452,7 @@ __global__ void __launch_bounds__(256) quant_act_dual_kernel(const uint16_t* __r
     }
     uint32_t lo, hi, sf;
     const int64_t kb = gc >> 4;
-    encode_block<SR_R>(v, g_r, (uint64_t)gr * ctr.pitch_r + ctr.base_r + (uint64_t)kb, seed_r, offset, lo, hi, sf);
+    encode_block<SR_R>(v, g_r, (uint64_t)gr * ctr.pitch_r + ctr.base_r + (uint64_t)kb, keys_r, offset, lo, hi, sf);
     *reinterpret_cast<uint2*>(q_rows + gr * (cols >> 1) + kb * 8) = make_uint2(lo, hi);
     sf_rows[sf_offset(gr, kb, ((cols >> 4) + 3) >> 2)] = (uint8_t)sf;
   }
@@ -438,7 +468,7 @@ __global__ void __launch_bounds__(256) quant_act_dual_kernel(const uint16_t* __r
     hadamard16_inplace(u);
     uint32_t lo, hi, sf;
     const int64_t kb = orow0 >> 4;
-    encode_block<SR_C>(u, g_c, (uint64_t)oc * ctr.pitch_c + ctr.base_c + (uint64_t)kb, seed_c, offset, lo, hi, sf);
+    encode_block<SR_C>(u, g_c, (uint64_t)oc * ctr.pitch_c + ctr.base_c + (uint64_t)kb, keys_c, offset, lo, hi, sf);
     *reinterpret_cast<uint2*>(q_cols + oc * (rows >> 1) + kb * 8) = make_uint2(lo, hi);
     sf_cols[sf_offset(oc, kb, ((rows >> 4) + 3) >> 2)] = (uint8_t)sf;
   }
@@ -559,11 +589,12 @@ extern "C" int nvfp4_quantize_shard_bf16(const void* x, int64_t rows, int64_t co
   }
   const uint16_t* xp = static_cast<const uint16_t*>(x);
   const bool sr = mode == NVFP4_ROUND_STOCHASTIC;
+  const PhiloxKeys keys = make_philox_keys(seed);
   if (!transpose) {
     const int bpr = (int)(cols >> 4);
     const int grid = grid_for(rows * bpr, 256, 1 << 30);
 #define NVFP4_LAUNCH_ROWS(SR_, RHT_) \
-    quant_rows_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, bpr, ld, signs16, amax, seed, offset, qdata, scales, pts_out, counter_pitch, counter_base)
+    quant_rows_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, bpr, ld, signs16, amax, keys, offset, qdata, scales, pts_out, counter_pitch, counter_base)
     if (sr && rht) NVFP4_LAUNCH_ROWS(true, true);
     else if (sr) NVFP4_LAUNCH_ROWS(true, false);
     else if (rht) NVFP4_LAUNCH_ROWS(false, true);
@@ -573,7 +604,7 @@ extern "C" int nvfp4_quantize_shard_bf16(const void* x, int64_t rows, int64_t co
     dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
     if (grid.y > 65535u) return NVFP4_E_SHAPE;
 #define NVFP4_LAUNCH_COLS(SR_, RHT_) \
-    quant_cols_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax, seed, offset, qdata, scales, pts_out, counter_pitch, counter_base)
+    quant_cols_kernel<SR_, RHT_><<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax, keys, offset, qdata, scales, pts_out, counter_pitch, counter_base)
     if (sr && rht) NVFP4_LAUNCH_COLS(true, true);
     else if (sr) NVFP4_LAUNCH_COLS(true, false);
     else if (rht) NVFP4_LAUNCH_COLS(false, true);
@@ -657,9 +688,10 @@ extern "C" int nvfp4_quantize_dual_bf16(const void* x, int64_t rows, int64_t col
   if (grid.y > 65535u) return NVFP4_E_LIMIT;
   const uint16_t* xp = static_cast<const uint16_t*>(x);
   const bool sr_r = mode_rows == NVFP4_ROUND_STOCHASTIC, sr_c = mode_cols == NVFP4_ROUND_STOCHASTIC;
+  const PhiloxKeys keys_r = make_philox_keys(seed_rows), keys_c = make_philox_keys(seed_cols);
 #define NVFP4_LAUNCH_DUAL(R_, C_) \
-  quant_act_dual_kernel<R_, C_><<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax_rows, amax_cols, seed_rows, \
-      seed_cols, offset, ctr, qdata_rows, scales_rows, pts_rows, qdata_cols, scales_cols, pts_cols)
+  quant_act_dual_kernel<R_, C_><<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax_rows, amax_cols, keys_r, \
+      keys_c, offset, ctr, qdata_rows, scales_rows, pts_rows, qdata_cols, scales_cols, pts_cols)
   if (sr_r && sr_c) NVFP4_LAUNCH_DUAL(true, true);
   else if (sr_r) NVFP4_LAUNCH_DUAL(true, false);
   else if (sr_c) NVFP4_LAUNCH_DUAL(false, true);
