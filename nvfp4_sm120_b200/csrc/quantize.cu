@@ -121,7 +121,9 @@ __global__ void __launch_bounds__(512) amax_plain_kernel(const uint16_t* __restr
     const uint32_t a = __vimax3_u16x2(q.x & k, q.y & k, q.z & k);
     m = __vimax3_u16x2(a, q.w & k, m);                 // both 16-bit halves of m carry a running maximum
   };
+  const bool flat = ld == (int64_t)vec_per_row * 8;      // contiguous rows: no division per load
   auto load = [&](int64_t i) {
+    if (flat) return __ldg(reinterpret_cast<const uint4*>(x) + i);
     const int64_t r = i / vec_per_row;
     const int cv = (int)(i - r * vec_per_row);
     return __ldg(reinterpret_cast<const uint4*>(x + r * ld) + cv);
