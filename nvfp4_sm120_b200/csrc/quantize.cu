@@ -223,9 +223,30 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint16_t* __restr
 // that a warp reads 128 contiguous bytes per row and each thread writes 32 contiguous output
 // bytes per column.
 // ---------------------------------------------------------------------------------------
+// The 16-point butterfly of two adjacent columns at once: (v0[i], v1[i]) ride in the two lanes of the
+// packed fp32 add / sub / fma, half the instructions of two scalar butterflies and the same bits
+// (same operations in the same order as hadamard16_inplace, exact zeros made +0).
+__device__ __forceinline__ void hadamard16_pair(float (&v0)[16], float (&v1)[16]) {
+#pragma unroll
+  for (int s = 1; s < 16; s <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      if ((i & s) == 0) fused::addsub2(v0[i], v1[i], v0[i | s], v1[i | s]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) fused::mul2_poszero(v0[i], v1[i], 0.25f, v0[i], v1[i]);
+}
+
+// sign-bit masks of the 16 rows for a packed bf16 pair (both halves of a word belong to one row)
+__device__ __forceinline__ void sign_masks(const float (&sg)[16], uint32_t (&sm)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) sm[i] = sg[i] < 0.0f ? 0x80008000u : 0u;
+}
+
 template <bool RHT>
 __device__ __forceinline__ void load_col_pair_block(const uint16_t* __restrict__ x, int64_t ld,
-                                                    int64_t r0, int64_t c, const float (&sg)[16],
+                                                    int64_t r0, int64_t c, const uint32_t (&sm)[16],
                                                     float (&v0)[16], float (&v1)[16]) {
   const uint32_t* p = reinterpret_cast<const uint32_t*>(x + r0 * ld + c);
   uint32_t w[16];
@@ -233,11 +254,11 @@ __device__ __forceinline__ void load_col_pair_block(const uint16_t* __restrict__
   for (int i = 0; i < 16; ++i) w[i] = __ldg(p + (size_t)i * (size_t)(ld >> 1));
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
-    v0[i] = bf16_lo(w[i]);
-    v1[i] = bf16_hi(w[i]);
-    if (RHT) { v0[i] *= sg[i]; v1[i] *= sg[i]; }
+    const uint32_t u = RHT ? (w[i] ^ sm[i]) : w[i];      // times +-1 = a flip of the sign bit
+    v0[i] = bf16_lo(u);
+    v1[i] = bf16_hi(u);
   }
-  if (RHT) { hadamard16_inplace(v0); hadamard16_inplace(v1); }
+  if (RHT) hadamard16_pair(v0, v1);
 }
 
 __global__ void __launch_bounds__(256) amax_rht_cols_kernel(const uint16_t* __restrict__ x, int64_t rows,
@@ -246,6 +267,8 @@ __global__ void __launch_bounds__(256) amax_rht_cols_kernel(const uint16_t* __re
                                                             float* __restrict__ amax) {
   float sg[16];
   load_signs(signs16, sg);
+  uint32_t sm[16];
+  sign_masks(sg, sm);
   const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
   const int64_t r_base = (int64_t)blockIdx.y * 64;
   float m = 0.0f;
@@ -255,7 +278,7 @@ __global__ void __launch_bounds__(256) amax_rht_cols_kernel(const uint16_t* __re
       const int64_t r0 = r_base + 16 * j;
       if (r0 >= rows) break;
       float v0[16], v1[16];
-      load_col_pair_block<true>(x, ld, r0, c, sg, v0, v1);
+      load_col_pair_block<true>(x, ld, r0, c, sm, v0, v1);
 #pragma unroll
       for (int i = 0; i < 16; ++i) m = fmaxf(m, fmaxf(fabsf(v0[i]), fabsf(v1[i])));
     }
@@ -278,8 +301,15 @@ __global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restr
   __shared__ float recip_tab[128];
   const GlobalScale g = global_scale(amax, recip_tab);
   if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && pts_out != nullptr) *pts_out = g.pts;
-  float sg[16];
-  if (RHT) load_signs(signs16, sg);
+  uint32_t sm[16];
+  if (RHT) {
+    float sg[16];
+    load_signs(signs16, sg);
+    sign_masks(sg, sm);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) sm[i] = 0u;
+  }
   const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
   if (c >= cols) return;
   const int64_t r_base = (int64_t)blockIdx.y * 64;
@@ -294,7 +324,7 @@ __global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restr
     const int64_t r0 = r_base + 16 * j;
     if (r0 < rows) {
       float v0[16], v1[16];
-      load_col_pair_block<RHT>(x, ld, r0, c, sg, v0, v1);
+      load_col_pair_block<RHT>(x, ld, r0, c, sm, v0, v1);
       const uint64_t kb = (uint64_t)(r0 >> 4);
       uint32_t sf0, sf1;
       encode_block<SR>(v0, g, (uint64_t)c * ctr_pitch + ctr_base + kb, keys, offset, q[0][2 * j], q[0][2 * j + 1], sf0);
@@ -483,6 +513,8 @@ __global__ void __launch_bounds__(256) amax_both_cols_kernel(const uint16_t* __r
                                                              float* __restrict__ maxima2) {
   float sg[16];
   load_signs(signs16, sg);
+  uint32_t sm[16];
+  sign_masks(sg, sm);
   const int64_t c = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
   const int64_t r_base = (int64_t)blockIdx.y * 64;
   float m = 0.0f;
@@ -497,17 +529,18 @@ __global__ void __launch_bounds__(256) amax_both_cols_kernel(const uint16_t* __r
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
         const uint32_t w = __ldg(p + (size_t)i * (size_t)(ld >> 1));
-        mp = max(mp, max(w & 0x7fffu, (w >> 16) & 0x7fffu));
-        v0[i] = bf16_lo(w) * sg[i];
-        v1[i] = bf16_hi(w) * sg[i];
+        mp = __vimax3_u16x2(mp, w & 0x7fff7fffu, 0u);          // both halves carry a running maximum
+        const uint32_t u = w ^ sm[i];
+        v0[i] = bf16_lo(u);
+        v1[i] = bf16_hi(u);
       }
-      hadamard16_inplace(v0);
-      hadamard16_inplace(v1);
+      hadamard16_pair(v0, v1);
 #pragma unroll
       for (int i = 0; i < 16; ++i) m = fmaxf(m, fmaxf(fabsf(v0[i]), fabsf(v1[i])));
     }
   }
   m = warp_max(m);
+  mp = max(mp & 0xffffu, mp >> 16);
   const float fp = warp_max(__uint_as_float(mp << 16));
   if ((threadIdx.x & 31) == 0) {
     atomic_max_nonneg(maxima2, fp);
