@@ -354,6 +354,104 @@ __global__ void __launch_bounds__(256) quant_cols_kernel(const uint16_t* __restr
   }
 }
 
+
+// ---------------------------------------------------------------------------------------
+// Wide form of the column MAXIMUM kernels for 16-byte rows (cols % 8 == 0).  The narrow kernels above read
+// 128 contiguous bytes of a row per warp instruction; here a CTA takes tiles of 16 rows x 512 columns
+// the way the activation kernels do (csrc/swiglu.cu): thread t and step k load the eight columns
+// 8 * (t % 64) of row 4k + t / 64 with one 16-byte load (a warp moves 512 contiguous bytes of a row),
+// the tile goes to padded shared memory, and thread t then reads its two columns of all 16 rows from
+// there (consecutive lanes, consecutive banks), with the next tile's loads in flight.  Measured on a
+// B200 at 4096 x 4096: both maxima 14.9 us against 17.1 us.  The same staging for the quantizer itself
+// was slower (116 us against 89.5 us at 4096 x 28672, RHT + stochastic): its long encode phase leaves
+// only the four prefetch loads per thread in flight, so quant_cols_kernel keeps its direct loads.
+// ---------------------------------------------------------------------------------------
+constexpr int kWideCols = 512;
+constexpr int kWidePitch = kWideCols / 2 + 4;            // 32-bit words per tile row, padded
+
+struct WideTile {
+  int64_t c0, r_base, c;        // first column of the CTA, first row of its 64, this thread's column pair
+  int cc, lr;                   // load role: eight columns at cc, row 4k + lr of a tile
+  bool col_in, mine;
+};
+__device__ __forceinline__ WideTile wide_tile(int64_t cols) {
+  WideTile t;
+  t.c0 = (int64_t)blockIdx.x * kWideCols;
+  t.r_base = (int64_t)blockIdx.y * 64;
+  t.cc = (threadIdx.x & 63) * 8;
+  t.lr = threadIdx.x >> 6;
+  t.col_in = t.c0 + t.cc < cols;
+  t.c = t.c0 + 2 * (int64_t)threadIdx.x;
+  t.mine = t.c < cols;
+  return t;
+}
+__device__ __forceinline__ void wide_fetch(const uint16_t* __restrict__ x, int64_t rows, int64_t ld, const WideTile& t,
+                                           int j, uint4 (&d)[4]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t r = t.r_base + 16 * j + 4 * k + t.lr;
+    d[k] = (t.col_in && r < rows) ? __ldg(reinterpret_cast<const uint4*>(x + r * ld + t.c0 + t.cc))
+                                  : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+__device__ __forceinline__ void wide_stage(uint32_t* tile, const WideTile& t, const uint4 (&d)[4]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4*>(&tile[(4 * k + t.lr) * kWidePitch + (t.cc >> 1)]) = d[k];
+}
+
+// BOTH: maxima2[0] = plain maximum as well (else only maxima2[0] = maximum after the transform)
+template <bool BOTH>
+__global__ void __launch_bounds__(256) amax_cols_wide_kernel(const uint16_t* __restrict__ x, int64_t rows, int64_t cols,
+                                                             int64_t ld, const float* __restrict__ signs16,
+                                                             float* __restrict__ out) {
+  __shared__ __align__(16) uint32_t tile[16 * kWidePitch];
+  float sg[16];
+  load_signs(signs16, sg);
+  uint32_t sm[16];
+  sign_masks(sg, sm);
+  const WideTile t = wide_tile(cols);
+  float m = 0.0f;
+  uint32_t mp = 0u;
+  uint4 nxt[4];
+  wide_fetch(x, rows, ld, t, 0, nxt);
+#pragma unroll 1
+  for (int j = 0; j < 4; ++j) {
+    if (t.r_base + 16 * j >= rows) break;                  // uniform over the CTA
+    wide_stage(tile, t, nxt);
+    if (BOTH) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t kk = 0x7fff7fffu;
+        mp = __vimax3_u16x2(mp, nxt[k].x & kk, nxt[k].y & kk);
+        mp = __vimax3_u16x2(mp, nxt[k].z & kk, nxt[k].w & kk);
+      }
+    }
+    if (j + 1 < 4) wide_fetch(x, rows, ld, t, j + 1, nxt);
+    __syncthreads();
+    if (t.mine) {
+      float v0[16], v1[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t u = tile[i * kWidePitch + threadIdx.x] ^ sm[i];
+        v0[i] = bf16_lo(u);
+        v1[i] = bf16_hi(u);
+      }
+      hadamard16_pair(v0, v1);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m = fmaxf(m, fmaxf(fabsf(v0[i]), fabsf(v1[i])));
+    }
+    __syncthreads();
+  }
+  m = warp_max(m);
+  if (BOTH) {
+    mp = max(mp & 0xffffu, mp >> 16);
+    const float fp = warp_max(__uint_as_float(mp << 16));
+    if ((threadIdx.x & 31) == 0) { atomic_max_nonneg(out, fp); atomic_max_nonneg(out + 1, m); }
+  } else {
+    if ((threadIdx.x & 31) == 0) atomic_max_nonneg(out, m);
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // weights: both layouts from one read.  A CTA takes a 64 x 64 tile of w [rows, cols]; thread
 // (row t / 4, segment t % 4) loads the 16 elements of row-wise block (row, segment) and leaves them in
@@ -582,7 +680,12 @@ extern "C" int nvfp4_amax_bf16(const void* x, int64_t rows, int64_t cols, int64_
     if ((rows & 15) != 0 || (cols & 1) != 0) return NVFP4_E_SHAPE;
     dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
     if (grid.y > 65535u) return NVFP4_E_SHAPE;
-    amax_rht_cols_kernel<<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax);
+    if ((cols & 7) == 0) {
+      const dim3 wgrid((unsigned)((cols + kWideCols - 1) / kWideCols), grid.y);
+      amax_cols_wide_kernel<false><<<wgrid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax);
+    } else {
+      amax_rht_cols_kernel<<<grid, 256, 0, stream>>>(xp, rows, cols, ld, signs16, amax);
+    }
   }
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
@@ -688,7 +791,12 @@ extern "C" int nvfp4_amax_both_bf16(const void* x, int64_t rows, int64_t cols, i
   if (zero_first && cudaMemsetAsync(maxima2, 0, 2 * sizeof(float), stream) != cudaSuccess) return NVFP4_E_LAUNCH;
   dim3 grid((unsigned)((cols / 2 + 255) / 256), (unsigned)((rows + 63) / 64));
   if (grid.y > 65535u) return NVFP4_E_LIMIT;
-  amax_both_cols_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), rows, cols, ld, signs16, maxima2);
+  if ((cols & 7) == 0) {
+    const dim3 wgrid((unsigned)((cols + kWideCols - 1) / kWideCols), grid.y);
+    amax_cols_wide_kernel<true><<<wgrid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), rows, cols, ld, signs16, maxima2);
+  } else {
+    amax_both_cols_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint16_t*>(x), rows, cols, ld, signs16, maxima2);
+  }
   return cudaGetLastError() == cudaSuccess ? NVFP4_OK : NVFP4_E_LAUNCH;
 }
 
