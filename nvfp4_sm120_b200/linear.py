@@ -117,7 +117,7 @@ class FP4LinearFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w, H, signs, wq_K, wq_N, amax_reduce=None, sharded=(False, False), x_amax=None,
-                x_amax_rht=True, dx_reduce=None, y_amax_out=None):
+                x_amax_rht=True, dx_reduce=None, y_amax_out=None, x_quant=None):
         # dx_reduce: optional callable(dx) -> handle with .wait(): starts the sum of the input gradient
         # over a tensor-parallel group right after the dgrad GEMM, so that it runs beside the wgrad
         # quantizations and GEMM; the handle is waited for before the backward returns
@@ -142,10 +142,16 @@ class FP4LinearFn(torch.autograd.Function):
         # x nor another pass in backward.  (A sharded x without producer maxima keeps the two-step path:
         # its maxima are reduced over the group one by one.)
         have_both = x_amax is not None and x_amax_rht and x_amax.numel() >= 2
-        dual = (_DUAL[0] and ctx.needs_input_grad[1] and x2.is_cuda and x2.shape[0] % BLK == 0
+        # (inside torch.no_grad() needs_input_grad still reflects requires_grad: ask the grad mode too)
+        dual = (_DUAL[0] and ctx.needs_input_grad[1] and torch.is_grad_enabled() and x2.is_cuda and x2.shape[0] % BLK == 0
                 and x2.numel() <= _DUAL_MAX_ELEMS and (x_red is None) and (have_both or not x_sharded))
         xtq = None
-        if dual:
+        if x_quant is not None:
+            # x_quant = quant_input(x, ...) made once by a caller that feeds x to several layers holding
+            # the same sign vector (q, k, v of a block): (row-wise operand, transformed transpose or None;
+            # without the transpose the backward quantizes x^T itself, as on the plain path)
+            xq, xtq = x_quant
+        elif dual:
             xq, xtq = quant_dual_nvfp4(x2, signs, None if x_amax is None else x_amax[0:1],
                                        x_amax[1:2] if have_both else None)
         else:
@@ -230,7 +236,7 @@ class FP4LinearFn(torch.autograd.Function):
             dw = nvfp4_mm(gtq, xtq.t(), _grad_dtype(w)).to(w.dtype)
         if pending is not None:
             pending.wait()
-        return dx, dw, None, None, None, None, None, None, None, None, None, None
+        return dx, dw, None, None, None, None, None, None, None, None, None, None, None
 
 
 def _quant(t, amax_reduce, stochastic=False, rht=False, H=None, signs=None, transpose=False, amax=None, counter=None):
@@ -298,18 +304,34 @@ class FP4Linear(nn.Module):
     def _wq_N(self):
         return self._cache.wq_N
 
-    def forward(self, x, amax=None, amax_signs=None, amax_out=None):
+    def quant_input(self, x, amax=None, amax_signs=None):
+        """Quantize x once for several FP4Linear layers that share this layer's sign vector (the q, k, v
+        projections of one normalized activation): returns what their `forward(x, x_quant=...)` takes.
+        With gradients on, that is the row-wise operand and the Hadamard-transformed transpose from one
+        read; without, the row-wise operand alone."""
+        if x.is_cuda and torch.is_autocast_enabled("cuda"):
+            x = x.to(torch.get_autocast_dtype("cuda"))
+        x2 = x.reshape(-1, x.shape[-1])
+        both = (amax is not None and amax.numel() >= 2 and x2.shape[0] % BLK == 0 and x2.dtype == torch.bfloat16
+                and (amax_signs is None or _same_signs(amax_signs, self.signs)))
+        plain = amax[0:1] if (amax is not None and x2.dtype == torch.bfloat16) else None
+        if torch.is_grad_enabled() and self.weight.requires_grad and x2.shape[0] % BLK == 0:
+            return quant_dual_nvfp4(x2, self.signs, plain, amax[1:2] if both else None)
+        return (quant_nvfp4(x2, amax=plain), None)
+
+    def forward(self, x, amax=None, amax_signs=None, amax_out=None, x_quant=None):
         """amax: optional fp32 [2] from a fused producer of x (see FP4LinearFn.forward), or fp32 [1] = the
         plain maximum alone; amax_signs: the sign vector its Hadamard maximum was computed with (None =
         this layer's own).  When it is not this layer's vector, only the plain maximum is used and the
         other is recomputed.  amax_out: optional fp32 [1] CUDA tensor the forward GEMM fills with max|y|
-        (bf16 activations), to be handed to the next layer as its `amax`."""
+        (bf16 activations), to be handed to the next layer as its `amax`.  x_quant: x already quantized by
+        `quant_input` of a layer with the same sign vector (amax is then not needed)."""
         if x.is_cuda and torch.is_autocast_enabled("cuda"):
             x = x.to(torch.get_autocast_dtype("cuda"))       # what autocast does for nn.Linear
         wq_K, wq_N = self._cache.get(self.weight)
         rht_ok = amax_signs is None or _same_signs(amax_signs, self.signs)
         return FP4LinearFn.apply(x, self.weight, self.H, self.signs, wq_K, wq_N, None, (False, False), amax, rht_ok,
-                                 None, amax_out)
+                                 None, amax_out, x_quant)
 
     def extra_repr(self):
         return f"in_features={self.weight.shape[1]}, out_features={self.weight.shape[0]}, bias=False, nvfp4"

@@ -89,8 +89,14 @@ class DecoderBlock(nn.Module):
         h, h_max = self._norm(self.norm_attn, x, self.q)
         split = lambda t, n: t.view(B, T, n, self.head_dim).transpose(1, 2)
         if h_max is not None:
-            kw = dict(amax=h_max, amax_signs=self.q.signs)
-            q, k, v = self.q(h, **kw), self.k(h, **kw), self.v(h, **kw)
+            from .linear import _same_signs
+            if _same_signs(self.q.signs, self.k.signs) and _same_signs(self.q.signs, self.v.signs):
+                # one quantization of h (both layouts) serves the three projections
+                hq = self.q.quant_input(h, h_max, self.q.signs)
+                q, k, v = self.q(h, x_quant=hq), self.k(h, x_quant=hq), self.v(h, x_quant=hq)
+            else:
+                kw = dict(amax=h_max, amax_signs=self.q.signs)
+                q, k, v = self.q(h, **kw), self.k(h, **kw), self.v(h, **kw)
         else:
             q, k, v = self.q(h), self.k(h), self.v(h)
         q, k, v = split(q, self.n_heads), split(k, self.n_kv), split(v, self.n_kv)

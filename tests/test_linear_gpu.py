@@ -163,3 +163,36 @@ def test_chained_linears_pass_the_maximum_through_the_gemm_epilogue(Q):
 
     for a, b in zip(run(True), run(False)):
         assert torch.equal(a, b)
+
+
+def test_shared_input_quantization_equals_per_layer_quantization(Q):
+    """quant_input: one quantization of an activation (both layouts) handed to several layers through
+    x_quant= gives the outputs and gradients of the layers quantizing it themselves, bit for bit; without
+    gradients (evaluation) only the row-wise operand is made."""
+    from nvfp4_sm120_b200 import quant
+    torch.manual_seed(12)
+    a, b = Q.FP4Linear(256, 128), Q.FP4Linear(256, 384)
+    for tokens in (192, 224):
+        x0 = torch.randn(tokens, 256, device="cuda", dtype=torch.bfloat16)
+        ga = torch.randn(tokens, 128, device="cuda", dtype=torch.bfloat16)
+        gb = torch.randn(tokens, 384, device="cuda", dtype=torch.bfloat16)
+
+        def run(shared):
+            for l in (a, b):
+                l.weight.grad = None
+            quant._SEED[0] = 700
+            x = x0.clone().requires_grad_(True)
+            if shared:
+                xq = a.quant_input(x)
+                assert xq[1] is not None
+                ya, yb = a(x, x_quant=xq), b(x, x_quant=xq)
+            else:
+                ya, yb = a(x), b(x)
+            torch.autograd.backward([ya, yb], [ga, gb])
+            return ya.detach(), yb.detach(), x.grad, a.weight.grad.clone(), b.weight.grad.clone()
+
+        for u, v in zip(run(True), run(False)):
+            assert torch.equal(u, v)
+    with torch.no_grad():
+        xq = a.quant_input(x0)
+        assert xq[1] is None and torch.equal(a(x0, x_quant=xq), a(x0))
